@@ -5,8 +5,9 @@ need (same kv heads, head size and window) form a *group*; a group has a page
 pool of its own and every request has one block table per group, so one page
 id covers the same ``page_size`` positions in every layer of the group.  Pages
 go back to the pool when the request ends, or, in a windowed group, as soon as
-every position on them lies behind the window of all queries still to come;
-freed pages are reused at once (last freed, first reused).
+every position on them lies behind the window of all queries still to come
+(pages that hold one of the group's first ``keep_first`` positions stay: windowed
+queries keep reading those); freed pages are reused at once (last freed, first reused).
 
 Beside the pages every request holds one *slot*: the index of its fixed-size
 state (the conv history of every conv layer, or whatever state a mixer
@@ -89,6 +90,7 @@ class PagedGroupSpec:
 
     name: str
     window: Optional[int] = None      # None: every earlier key is kept
+    keep_first: int = 0               # with a window: the first positions whose pages are never given back
 
 
 class _PoolView:
@@ -136,6 +138,11 @@ class CacheManager:
         self._cm = ctypes.c_void_p(self._lib.gesso_cm_new(G, windows, page_size, pages, num_slots, max_positions))
         if not self._cm:
             raise invalid("cache manager: sizes out of range")
+        for i, g in enumerate(self.groups):
+            if g.keep_first < 0:
+                raise invalid(f"group {g.name}: keep_first must be >= 0")
+            if g.keep_first and g.window is not None:
+                self._lib.gesso_cm_set_keep_first(self._cm, i, int(g.keep_first))
         self.pools = [_PoolView(self, i, c) for i, c in enumerate(counts)]
         self.slots = _PoolView(self, -1, num_slots)
         self._handle: Dict[Hashable, int] = {}          # request id -> native handle

@@ -1,7 +1,7 @@
 """One registry from an architecture's name to the adapter that reads its config.
 
-``config.json`` names its model class in ``architectures[0]`` (``model_type``
-is the fallback key).  An adapter turns the parsed JSON object into a
+``config.json`` names its model class in ``architectures[0]`` (or in a plain
+``architecture`` string; ``model_type`` is the fallback key).  An adapter turns the parsed JSON object into a
 :class:`~gesso_b200.config.spec.ModelSpec`.  An unknown name is refused with
 the list of known names, as the reference's adapter table does
 (src/Inference/arch_adapters.jl:1075-1109).
@@ -58,6 +58,8 @@ def architecture_name(config: Mapping[str, Any]) -> str:
     archs = config.get("architectures")
     if isinstance(archs, (list, tuple)) and len(archs) >= 1 and isinstance(archs[0], str):
         return archs[0]
+    if isinstance(config.get("architecture"), str):      # some configurations name one class, not a list
+        return config["architecture"]
     mt = config.get("model_type")
     if isinstance(mt, str):
         for name in _ARCHITECTURES:
@@ -67,7 +69,7 @@ def architecture_name(config: Mapping[str, Any]) -> str:
             f"config.json: model_type {mt!r} is not registered; known architectures: "
             f"{known_architectures()}"
         )
-    raise invalid("config.json: neither 'architectures' nor 'model_type' names a model class")
+    raise invalid("config.json: neither 'architectures', 'architecture' nor 'model_type' names a model class")
 
 
 def spec_from_config(config: Mapping[str, Any]) -> ModelSpec:

@@ -42,10 +42,13 @@ class BlockSpec:
 
     arrangement: str                 # registered block arrangement, e.g. "prenorm"
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]     # None: a layer without a feed-forward (arrangements that allow it)
     mixer_norm: PartSpec
-    ff_norm: PartSpec
+    ff_norm: Optional[PartSpec]
     prefix: str
+    # norms of a sublayer's OUTPUT, before it is added to the stream (the "sandwich" arrangement)
+    mixer_post_norm: Optional[PartSpec] = None
+    ff_post_norm: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)

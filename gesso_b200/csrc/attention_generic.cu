@@ -8,6 +8,12 @@
 // of values are float32 with a running maximum per lane (lanes stride over keys) that is
 // merged across the warp at the end, so the result does not depend on which pages hold the keys
 // or on what else is in the batch.
+//
+// Options, all off by default: values of another width than the keys (`vd`); a window that also keeps the
+// first `keep_first` positions of the sequence visible (key u is read if u <= p and (p - u < window or
+// u < keep_first)); a caller's scale instead of 1/sqrt(hd) (the scale is always passed in); an output gate:
+// the result is multiplied by sigmoid(gate[t, h * vd + j]) before it is stored (`gate` rows are
+// `gate_stride` elements apart, e.g. further columns of the fused projection).
 #include <math.h>
 
 #include "common.cuh"
@@ -18,7 +24,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
                                const T* __restrict__ v_pages, const int* __restrict__ block_table,
                                int max_pages, int page_size, const int* __restrict__ positions,
                                const int* __restrict__ seg_of_token, T* __restrict__ out, int n_tokens,
-                               int nh, int nkv, int hd, int window, float scale) {
+                               int nh, int nkv, int hd, int window, float scale, int vd, int keep_first,
+                               const T* __restrict__ gate, int gate_stride) {
     __shared__ float q_s[4][HD_PAD];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const long long wi = (long long)blockIdx.x * 4 + wid;
@@ -37,12 +44,15 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
 #pragma unroll
     for (int j = 0; j < HD_PAD; ++j) acc[j] = 0.f;
 
-    for (int u = lo + lane; u <= pos; u += 32) {
+    // with a window, the kept first positions come first (lanes stride over them), then the window itself
+    const int n_kept = lo > 0 ? min(keep_first, lo) : 0;
+    for (int uu = lane; uu < n_kept + (pos - lo + 1); uu += 32) {
+        const int u = uu < n_kept ? uu : lo + (uu - n_kept);
         const int page = bt[u / page_size];
         if (page < 0) continue;
         const T* kr = k_pages + (((size_t)page * nkv + kvh) * page_size + (u % page_size)) * hd;
         // V is stored [feature][slot] inside a page
-        const T* vr = v_pages + ((size_t)page * nkv + kvh) * hd * page_size + (u % page_size);
+        const T* vr = v_pages + ((size_t)page * nkv + kvh) * vd * page_size + (u % page_size);
         float dot = 0.f;
 #pragma unroll
         for (int j = 0; j < HD_PAD; ++j)
@@ -59,35 +69,41 @@ paged_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k_
         l += p;
 #pragma unroll
         for (int j = 0; j < HD_PAD; ++j)
-            if (j < hd) acc[j] += p * to_f32(vr[(size_t)j * page_size]);
+            if (j < vd) acc[j] += p * to_f32(vr[(size_t)j * page_size]);
     }
     const float M = warp_max(m);
     const float f = (m == -INFINITY) ? 0.f : expf(m - M);
     const float L = warp_sum(l * f);
-    T* orow = out + ((size_t)t * nh + h) * hd;
+    T* orow = out + ((size_t)t * nh + h) * vd;
+    const T* grow = gate ? gate + (size_t)t * gate_stride + (size_t)h * vd : nullptr;
 #pragma unroll
     for (int j = 0; j < HD_PAD; ++j) {
         const float a = warp_sum(acc[j] * f);
-        if (j < hd && (j & 31) == lane) orow[j] = from_f32<T>(a / L);
+        if (j < vd && (j & 31) == lane) {
+            float y = a / L;
+            if (grow) y *= 1.f / (1.f + expf(-to_f32(grow[j])));
+            orow[j] = from_f32<T>(y);
+        }
     }
 }
 
 template <typename T>
 static int launch_generic(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
                           int max_pages, int page_size, const int* positions, const int* seg_of_token,
-                          void* out, int n_tokens, int nh, int nkv, int hd, int window, float scale,
-                          cudaStream_t stream) {
+                          void* out, int n_tokens, int nh, int nkv, int hd, int window, float scale, int vd,
+                          int keep_first, const void* gate, int gate_stride, cudaStream_t stream) {
     const long long total = (long long)n_tokens * nh;
     const long long blocks = (total + 3) / 4;
     if (blocks > 2147483647LL) return GESSO_ERR_BAD_SIZE;
 #define GO(PAD)                                                                                          \
     paged_attention_generic_kernel<T, PAD><<<(unsigned)blocks, 128, 0, stream>>>(                        \
         (const T*)q, (const T*)k_pages, (const T*)v_pages, block_table, max_pages, page_size, positions, \
-        seg_of_token, (T*)out, n_tokens, nh, nkv, hd, window, scale)
-    if (hd <= 32) GO(32);
-    else if (hd <= 64) GO(64);
-    else if (hd <= 128) GO(128);
-    else if (hd <= 256) GO(256);
+        seg_of_token, (T*)out, n_tokens, nh, nkv, hd, window, scale, vd, keep_first, (const T*)gate, gate_stride)
+    const int wide = hd > vd ? hd : vd;
+    if (wide <= 32) GO(32);
+    else if (wide <= 64) GO(64);
+    else if (wide <= 128) GO(128);
+    else if (wide <= 256) GO(256);
     else return GESSO_ERR_BAD_SIZE;
 #undef GO
     return launch_status();
@@ -97,14 +113,19 @@ GESSO_API int gesso_paged_attention_generic(const void* q, const void* k_pages, 
                                             const int* block_table, int max_pages, int page_size,
                                             const int* positions, const int* seg_of_token, void* out,
                                             int n_tokens, int nh, int nkv, int hd, int window, float scale,
+                                            int vd, int keep_first, const void* gate, int gate_stride,
                                             cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || hd <= 0 || page_size <= 0) return GESSO_ERR_BAD_SIZE;
+    if (vd <= 0) vd = hd;
+    if (keep_first < 0 || (gate && gate_stride < nh * vd)) return GESSO_ERR_BAD_SIZE;
     if (dtype == GESSO_F32)
         return launch_generic<float>(q, k_pages, v_pages, block_table, max_pages, page_size, positions,
-                                     seg_of_token, out, n_tokens, nh, nkv, hd, window, scale, stream);
+                                     seg_of_token, out, n_tokens, nh, nkv, hd, window, scale, vd, keep_first, gate,
+                                     gate_stride, stream);
     if (dtype == GESSO_BF16)
         return launch_generic<bf16>(q, k_pages, v_pages, block_table, max_pages, page_size, positions,
-                                    seg_of_token, out, n_tokens, nh, nkv, hd, window, scale, stream);
+                                    seg_of_token, out, n_tokens, nh, nkv, hd, window, scale, vd, keep_first, gate,
+                                    gate_stride, stream);
     return GESSO_ERR_BAD_DTYPE;
 }

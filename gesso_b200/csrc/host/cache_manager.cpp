@@ -73,6 +73,7 @@ struct Request {
 
 struct Manager {
     std::vector<int> windows;              // per group: 0 = every earlier key is kept
+    std::vector<int> keep_first;           // per group: the first positions a windowed query keeps reading
     int page_size = 1, max_positions = 1, max_pages = 1;
     std::vector<Pool> pools;
     Pool slots;
@@ -122,12 +123,21 @@ HOST_API void* gesso_cm_new(int n_groups, const int* windows, int page_size, con
     for (int g = 0; g < n_groups; ++g) {
         if (windows[g] < 0 || num_pages[g] < 0) { delete m; return nullptr; }
         m->windows.push_back(windows[g]);
+        m->keep_first.push_back(0);
         m->pools.emplace_back(num_pages[g]);
     }
     m->slots = Pool(num_slots);
     return m;
 }
 HOST_API void gesso_cm_delete(void* cm) { delete static_cast<Manager*>(cm); }
+
+// the pages that hold the first `keep` positions of a windowed group's sequences are never given back early
+HOST_API int gesso_cm_set_keep_first(void* cm, int group, int keep) {
+    Manager* m = static_cast<Manager*>(cm);
+    if (group < 0 || group >= (int)m->keep_first.size() || keep < 0) return E_BAD_ARG;
+    m->keep_first[group] = keep;
+    return OK;
+}
 
 HOST_API int gesso_cm_admit(void* cm, int64_t rid) {
     Manager* m = static_cast<Manager*>(cm);
@@ -227,7 +237,7 @@ HOST_API int gesso_cm_commit(void* cm, int64_t rid, int n_new) {
         const int first_needed = r->length - m->windows[g] + 1;
         int dead = (first_needed > 0 ? first_needed : 0) / m->page_size;
         if (dead > r->n_pages[g]) dead = r->n_pages[g];
-        for (int i = 0; i < dead; ++i)
+        for (int i = m->pages_for(m->keep_first[g]); i < dead; ++i)
             if (r->rows[g][i] != FREED) {
                 const int e = m->pools[g].release(r->rows[g][i]);
                 if (e < 0) return e;

@@ -83,6 +83,7 @@ _SIGNATURES = {
     "gesso_pool_is_held": ([c_void_p, c_int], c_int),
     "gesso_cm_new": ([c_int, _IP, c_int, _IP, c_int, c_int], c_void_p),
     "gesso_cm_delete": ([c_void_p], None),
+    "gesso_cm_set_keep_first": ([c_void_p, c_int, c_int], c_int),
     "gesso_cm_admit": ([c_void_p, c_int64], c_int),
     "gesso_cm_release": ([c_void_p, c_int64], c_int),
     "gesso_cm_info": ([c_void_p, c_int64, _IP], c_int),

@@ -24,6 +24,10 @@
 // the tables are [max_positions, rot_dim/2] then.  The kernel that works by 64-token tiles takes the
 // full half-split layout only; everything else goes through the one below.
 //
+// The projection may carry biases (a float32 vector along the fused row, added before norm and rotation, and
+// to v), values of another width than the keys (`vd`), and further columns behind the v heads that this
+// kernel leaves alone (`row_stride` elements per token); the per-token kernel takes all of these.
+//
 // One warp per (token, head).  Everything is float32 inside; stores round to the run type.
 #include "common.cuh"
 
@@ -33,7 +37,8 @@ __global__ void qk_norm_rope_store_kernel(
     const float* __restrict__ cos_t, const float* __restrict__ sin_t, const int* __restrict__ positions,
     const int* __restrict__ seg_of_token, const int* __restrict__ block_table, int max_pages, int page_size,
     T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages, int n_tokens, int nh, int nkv,
-    int hd, int write_kv, int rot_dim, int interleaved, int* __restrict__ status) {
+    int hd, int write_kv, int rot_dim, int interleaved, int* __restrict__ status,
+    const float* __restrict__ bias, int row_stride, int vd) {
     // let the successor in first (it only prefetches what no running kernel writes until its own wait)
     pdl_launch_dependents();
     pdl_wait();
@@ -43,10 +48,14 @@ __global__ void qk_norm_rope_store_kernel(
     if (wi >= (long long)n_tokens * heads) return;
     const int t = (int)(wi / heads), head = (int)(wi % heads);
     const int half = hd >> 1;
-    const T* src = qkv + (size_t)t * heads * hd + (size_t)head * hd;
+    const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
+    // a token's row: q heads, k heads (hd features each), v heads (vd features each), then whatever else
+    // the fused projection carries (row_stride elements in all); `bias` runs along the same row
+    const int col0 = (is_q || is_k) ? head * hd : (nh + nkv) * hd + (head - nh - nkv) * vd;
+    const T* src = qkv + (size_t)t * row_stride + col0;
+    const float* bs = bias ? bias + col0 : nullptr;
     const int pos = positions[t];
 
-    const bool is_q = head < nh, is_k = !is_q && head < nh + nkv;
     T* dst;
     if (is_q) {
         dst = q_out + ((size_t)t * nh + head) * hd;
@@ -62,12 +71,12 @@ __global__ void qk_norm_rope_store_kernel(
             // v is stored transposed inside its page, [head size][page size], so that the attention
             // kernels read the values of consecutive keys of one feature as one contiguous piece
             const int slot = pos % page_size;
-            T* vt = v_pages + ((size_t)page * nkv + kvh) * hd * page_size + slot;
+            T* vt = v_pages + ((size_t)page * nkv + kvh) * vd * page_size + slot;
             // the last token of its request in this step clears the rest of its 16-slot block
             const bool last = t == n_tokens - 1 || seg_of_token[t + 1] != s;
             const int clear = last ? min(page_size, ((slot >> 4) + 1) << 4) - slot : 1;
-            for (int j = lane; j < hd; j += 32) {
-                vt[(size_t)j * page_size] = src[j];
+            for (int j = lane; j < vd; j += 32) {
+                vt[(size_t)j * page_size] = bs ? from_f32<T>(to_f32(src[j]) + bs[j]) : src[j];
                 for (int z = 1; z < clear; ++z) vt[(size_t)j * page_size + z] = from_f32<T>(0.f);
             }
             return;
@@ -77,10 +86,10 @@ __global__ void qk_norm_rope_store_kernel(
     const float* w = is_q ? q_w : k_w;
     float ss = 0.f;
     for (int i = lane; i < half; i += 32) {
-        const float a = to_f32(src[i]), b = to_f32(src[i + half]);
+        const float a = to_f32(src[i]) + (bs ? bs[i] : 0.f), b = to_f32(src[i + half]) + (bs ? bs[i + half] : 0.f);
         ss += a * a + b * b;
     }
-    ss = warp_sum(ss);
+    if (w) ss = warp_sum(ss);
     const float denom = w ? sqrtf(ss / (float)hd + eps) : 1.f;
     const bool rotate = cos_t != nullptr;   // no table: the mixer has no position encoding
     const int rot_half = rotate ? rot_dim >> 1 : 0;
@@ -89,6 +98,7 @@ __global__ void qk_norm_rope_store_kernel(
     for (int i = lane; i < rot_half; i += 32) {            // the rotated pairs
         const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + rot_half;
         float a = to_f32(src[ia]), b = to_f32(src[ib]);
+        if (bs) { a += bs[ia]; b += bs[ib]; }
         if (w) { a = (a / denom) * w[ia]; b = (b / denom) * w[ib]; }
         const float c = cs[i], s = sn[i];
         dst[ia] = from_f32<T>(a * c - b * s);
@@ -96,6 +106,7 @@ __global__ void qk_norm_rope_store_kernel(
     }
     for (int i = 2 * rot_half + lane; i < hd; i += 32) {   // features the position part leaves alone
         float a = to_f32(src[i]);
+        if (bs) a += bs[i];
         if (w) a = (a / denom) * w[i];
         dst[i] = from_f32<T>(a);
     }
@@ -267,9 +278,13 @@ GESSO_API int gesso_qk_norm_rope_store(const void* qkv, int dtype, const float* 
                                        const int* seg_of_token, const int* block_table, int max_pages,
                                        int page_size, void* q_out, void* k_pages, void* v_pages, int n_tokens,
                                        int nh, int nkv, int hd, int write_kv, int rot_dim, int interleaved,
-                                       int* status, cudaStream_t stream) {
+                                       int* status, const float* bias, int row_stride, int vd,
+                                       cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (hd <= 0 || (hd & 1) || nh <= 0 || nkv <= 0 || page_size <= 0) return GESSO_ERR_BAD_SIZE;
+    if (vd <= 0) vd = hd;                                      // values as wide as keys
+    if (row_stride <= 0) row_stride = write_kv ? (nh + nkv) * hd + nkv * vd : nh * hd;
+    if (row_stride < (write_kv ? (nh + nkv) * hd + nkv * vd : nh * hd)) return GESSO_ERR_BAD_SIZE;
     if (cos_t != nullptr && (rot_dim < 2 || (rot_dim & 1) || rot_dim > hd)) return GESSO_ERR_BAD_SIZE;
     const int warps = 4;
     const long long total = (long long)n_tokens * (write_kv ? nh + 2 * nkv : nh);
@@ -279,12 +294,12 @@ GESSO_API int gesso_qk_norm_rope_store(const void* qkv, int dtype, const float* 
         launch_pdl(qk_norm_rope_store_kernel<float>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream,
             (const float*)qkv, q_w, k_w, eps, cos_t, sin_t, positions, seg_of_token, block_table, max_pages,
             page_size, (float*)q_out, (float*)k_pages, (float*)v_pages, n_tokens, nh, nkv, hd, write_kv, rot_dim,
-            interleaved, status);
+            interleaved, status, bias, row_stride, vd);
     else if (dtype == GESSO_BF16)
         launch_pdl(qk_norm_rope_store_kernel<bf16>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream,
             (const bf16*)qkv, q_w, k_w, eps, cos_t, sin_t, positions, seg_of_token, block_table, max_pages,
             page_size, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, n_tokens, nh, nkv, hd, write_kv, rot_dim,
-            interleaved, status);
+            interleaved, status, bias, row_stride, vd);
     else
         return GESSO_ERR_BAD_DTYPE;
     return launch_status();

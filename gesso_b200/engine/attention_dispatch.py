@@ -13,10 +13,14 @@ import torch
 from .. import ops
 
 
-def paged_attention(rt, q, cache, ctx, window, scale):
+def paged_attention(rt, q, cache, ctx, window, scale, keep_first: int = 0, gate=None):
     N, nh, hd = q.shape
     nkv, page_size = cache.k_pages.shape[1], cache.k_pages.shape[2]
-    if q.dtype == torch.bfloat16 and ops.fast_attention_takes(hd, page_size, nh, nkv):
+    vd = cache.v_pages.shape[2]
+    if window is None:
+        keep_first = 0                       # without a window every earlier key is visible anyway
+    plain = vd == hd and not keep_first and gate is None
+    if q.dtype == torch.bfloat16 and plain and ops.fast_attention_takes(hd, page_size, nh, nkv):
         if ctx.decode_only:
             splits = ops.decode_splits(ctx.n_segs, nkv, ctx.max_kv_len, uneven=True)
             ws = None
@@ -38,4 +42,4 @@ def paged_attention(rt, q, cache, ctx, window, scale):
         return ops.prefill_attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.seg_start,
                                      ctx.seg_pos0, ctx.tile_seg, ctx.tile_q0, window, scale)
     return ops.paged_attention_generic(q, cache.k_pages, cache.v_pages, cache.block_table,
-                                       ctx.positions, ctx.seg_of_token, window, scale)
+                                       ctx.positions, ctx.seg_of_token, window, scale, keep_first, gate)

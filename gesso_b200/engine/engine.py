@@ -58,8 +58,10 @@ class DeviceCache:
             # request's last position; the cache writer keeps those slots zero (qk_rope_store.cu), and
             # wholly masked pages are never read.  Zero-filled here only so that fresh memory is defined.
             # One page more than the manager hands out: the scratch page of padded steps.
-            self.kv.append(torch.zeros((len(owners), 2, max(pages, 1) + 1, need.n_kv_heads, page_size,
-                                        need.head_dim), dtype=dt, device=dev))
+            # Per owner all K pages [page][kv head][slot][feature], then all V pages [page][kv head][value
+            # feature][slot]; values may be of another width than keys.
+            per_page = need.n_kv_heads * page_size * (need.head_dim + need.value_dim)
+            self.kv.append(torch.zeros((len(owners), (max(pages, 1) + 1) * per_page), dtype=dt, device=dev))
         self.scratch_pages = [max(pages, 1) for pages in num_pages]
         self.scratch_slot = max(num_slots, 1)
         # One buffer for all fixed-size state, a slot's entries side by side (each padded to 128 bytes),
@@ -294,10 +296,12 @@ class Engine:
             for p in plans:
                 if p.kind == "paged":
                     kv = dc.kv[p.group][p.index]
-                    # K pages are [page, kv head, slot, feature]; V pages hold the same bytes as
-                    # [page, kv head, feature, slot]
-                    v = kv[1].view(kv.shape[1], kv.shape[2], kv.shape[4], kv.shape[3])
-                    views.append(PagedView(kv[0], v, ctx.block_tables[p.group], writes=(p.owner == e)))
+                    need = plan.paged_groups[p.group][0]
+                    pages = dc.scratch_pages[p.group] + 1
+                    nk = pages * need.n_kv_heads * self.page_size * need.head_dim
+                    k = kv[:nk].view(pages, need.n_kv_heads, self.page_size, need.head_dim)
+                    v = kv[nk:].view(pages, need.n_kv_heads, need.value_dim, self.page_size)
+                    views.append(PagedView(k, v, ctx.block_tables[p.group], writes=(p.owner == e)))
                 else:
                     views.append(StateView(dc.state[p.index], ctx.slots, writes=(p.owner == e)))
             out.append(None if not views else views[0] if plan.single[e] else tuple(views))

@@ -37,10 +37,10 @@ class Runtime:
         self.max_positions = int(max_positions)
         self.shared: Dict = {}
 
-    def attention(self, q, cache, ctx, window, scale):
+    def attention(self, q, cache, ctx, window, scale, keep_first: int = 0, gate=None):
         """Attention of the step's queries over the paged cache (kernel choice lives here)."""
         from . import attention_dispatch
-        return attention_dispatch.paged_attention(self, q, cache, ctx, window, scale)
+        return attention_dispatch.paged_attention(self, q, cache, ctx, window, scale, keep_first, gate)
 
 
 @dataclass
@@ -99,7 +99,8 @@ class CachePlan:
                 plans = []
                 for need, op in zip(needs, theirs):
                     same = (isinstance(need, PagedNeed) and op.kind == "paged"
-                            and (need.n_kv_heads, need.head_dim) == (op.need.n_kv_heads, op.need.head_dim)) or \
+                            and (need.n_kv_heads, need.head_dim, need.value_dim)
+                            == (op.need.n_kv_heads, op.need.head_dim, op.need.value_dim)) or \
                            (isinstance(need, StateNeed) and op.kind == "state"
                             and (need.shape, need.dtype) == (op.need.shape, op.need.dtype))
                     if not same:
@@ -110,6 +111,9 @@ class CachePlan:
                         # back would find them gone (and silently attend to fewer keys)
                         raise invalid(f"schedule entry {e}: reads the cache of entry {o} with a window of "
                                       f"{need.window or 'all'} keys, but that cache keeps only {op.need.window}")
+                    if isinstance(need, PagedNeed) and op.need.window is not None and need.keep_first > op.need.keep_first:
+                        raise invalid(f"schedule entry {e}: reads the first {need.keep_first} keys of the cache of "
+                                      f"entry {o}, which keeps only {op.need.keep_first} of them")
                     plans.append(CacheSlotPlan(op.kind, o, op.group, op.index, need))
                 self.entries.append(plans)
                 continue
@@ -128,7 +132,9 @@ class CachePlan:
             self.entries.append(plans)
 
     def group_specs(self) -> List[PagedGroupSpec]:
-        return [PagedGroupSpec(f"kv{n.n_kv_heads}x{n.head_dim}" + (f"w{n.window}" if n.window else ""), n.window)
+        return [PagedGroupSpec(f"kv{n.n_kv_heads}x{n.head_dim}" + (f"v{n.value_dim}" if n.v_head_dim else "")
+                               + (f"w{n.window}" if n.window else "") + (f"k{n.keep_first}" if n.keep_first else ""),
+                               n.window, n.keep_first)
                 for n, _ in self.paged_groups]
 
 
@@ -148,7 +154,7 @@ class Model:
         for b, blk in zip(spec.blocks, self.blocks):
             blk.bind({k[len(b.prefix):]: v for k, v in dev.items() if k.startswith(b.prefix)}, self.rt)
         self.final_norm = build_norm(spec.final_norm)
-        self.final_norm.bind({"weight": dev["final_norm.weight"]}, self.rt)
+        self.final_norm.bind({k[len("final_norm."):]: v for k, v in dev.items() if k.startswith("final_norm.")}, self.rt)
         self.embedding = dev["embedding.weight"]
         self.lm_head = self.embedding if spec.tie_embedding else dev["lm_head.weight"]
         self.cache_plan = CachePlan(spec, self.blocks)
@@ -169,7 +175,7 @@ class Model:
         if ctx.n_rows == 0:
             # the last sublayer's output is only needed by the head; nothing to return
             return None
-        if ctx.rows_are_all_tokens and pending[0] is None:
+        if ctx.rows_are_all_tokens and pending[0] is None and pending[1] is None:
             # every token's logits are wanted, in order: no gather, and the norm can ride in the
             # prologue of the head's matrix product
             if getattr(self.final_norm, "supports_lazy", False):

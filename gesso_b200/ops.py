@@ -118,6 +118,114 @@ def rmsnorm_rows(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Ten
     return out
 
 
+class DytParams:
+    """One Dynamic Tanh norm: ``tanh(alpha * x) * weight + bias`` (``alpha`` a Python float)."""
+
+    __slots__ = ("alpha", "weight", "bias")
+
+    def __init__(self, alpha: float, weight: torch.Tensor, bias: Optional[torch.Tensor]):
+        self.alpha, self.weight, self.bias = float(alpha), weight, bias
+
+
+class PostNormed:
+    """A sublayer's output that is normed before it is added to the residual stream: ``h += post(delta)``.
+    A norm that understands it does that add in the same pass as its own norm (``add_dyt``); any other
+    consumer calls :meth:`add_into` first and goes on with nothing pending."""
+
+    __slots__ = ("delta", "post", "bias")
+
+    def __init__(self, delta: torch.Tensor, post: DytParams, bias: Optional[torch.Tensor] = None):
+        self.delta, self.post, self.bias = delta, post, bias      # bias: a vector added to delta before the norm
+
+    def add_into(self, h: torch.Tensor) -> None:
+        add_dyt(h, self.delta, self.bias, self.post, None, None)
+
+
+def add_dyt(h: torch.Tensor, delta: Optional[torch.Tensor], delta_bias: Optional[torch.Tensor],
+            post: Optional[DytParams], pre: Optional[DytParams], out_dtype: Optional[torch.dtype],
+            rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """``h += post(delta (+ bias))`` in place (float32; ``post`` None: a plain add), returns ``pre(h)`` in
+    ``out_dtype`` (``pre`` None: nothing).  With ``rows`` only those rows are computed and ``h`` stays."""
+    _cuda_contig(h, "h", torch.float32)
+    N, H = h.shape
+    for p in (post, pre):
+        if p is not None:
+            _cuda_contig(p.weight, "norm weight", torch.float32)
+            _need(p.weight.numel() == H, "norm weight size differs from the row width")
+            if p.bias is not None:
+                _cuda_contig(p.bias, "norm bias", torch.float32)
+                _need(p.bias.numel() == H, "norm bias size differs from the row width")
+    if delta is not None:
+        _cuda_contig(delta, "delta")
+        _need(tuple(delta.shape) == (N, H), "delta shape differs from h")
+    if delta_bias is not None:
+        _cuda_contig(delta_bias, "delta_bias", torch.float32)
+        _need(delta is not None and delta_bias.numel() == H, "delta_bias needs a delta of the same width")
+    if rows is not None:
+        _cuda_contig(rows, "rows", torch.int32)
+    n_out = N if rows is None else rows.numel()
+    out = torch.empty((n_out, H), dtype=out_dtype, device=h.device) if pre is not None else None
+    _lib.check(_lib.library().gesso_add_dyt(
+        _p(h), _p(delta), _dt(delta) if delta is not None else F32, _p(delta_bias),
+        post.alpha if post else 0.0, _p(post.weight) if post else None, _p(post.bias) if post else None,
+        pre.alpha if pre else 0.0, _p(pre.weight) if pre else None, _p(pre.bias) if pre else None,
+        _p(out), _dt(out) if out is not None else F32, _p(rows), n_out, H, _stream()), "add_dyt")
+    return out
+
+
+# ---- routed feed-forward ---------------------------------------------------------------------
+MOE_SCORES = {"sigmoid": 0, "softmax": 1}
+MOE_ACTS = {"relu2": 0, "silu": 1, "gelu_tanh": 2}
+
+
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], top: int, n_groups: int,
+              keep_groups: int, group_top: int = 2, score: str = "sigmoid", renorm: bool = False,
+              weight_scale: float = 1.0):
+    """Router of a mixture of experts, float32: returns ``(expert ids int32 [N, top], weights float32 [N, top])``
+    in the order of the choice (best first)."""
+    _cuda_contig(x, "x")
+    _cuda_contig(w_router, "router weight", torch.float32)
+    N, H = x.shape
+    E = w_router.shape[0]
+    _need(w_router.shape[1] == H, "router width differs from the row width")
+    if correction is not None:
+        _cuda_contig(correction, "correction", torch.float32)
+        _need(correction.numel() == E, "one correction per expert")
+    idx = torch.empty((N, top), dtype=torch.int32, device=x.device)
+    w = torch.empty((N, top), dtype=torch.float32, device=x.device)
+    _lib.check(_lib.library().gesso_moe_route(
+        _p(x), _dt(x), _p(w_router), _p(correction), _p(idx), _p(w), N, H, E, int(top), int(n_groups), int(keep_groups),
+        int(group_top), MOE_SCORES[score], 1 if renorm else 0, float(weight_scale), _stream()), "moe_route")
+    return idx, w
+
+
+def moe_experts_pairs(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, idx: torch.Tensor, w: torch.Tensor,
+                      act: str = "relu2") -> torch.Tensor:
+    """``y[t] = sum_k w[t,k] * W_down[idx[t,k]] act(W_up[idx[t,k]] x[t])`` by (token, expert) pair; float32 [N, H].
+    ``w_up`` [E, F, K], ``w_down`` [E, H, F]."""
+    _cuda_contig(x, "x")
+    _cuda_contig(w_up, "w_up")
+    _cuda_contig(w_down, "w_down")
+    N, K = x.shape
+    E, F, K2 = w_up.shape
+    _need(K2 == K and tuple(w_down.shape[::2]) == (E, F), "expert matrices do not fit the rows")
+    Hout = w_down.shape[1]
+    top = idx.shape[1]
+    a = torch.empty((N * top, F), dtype=x.dtype, device=x.device)
+    y = torch.empty((N, Hout), dtype=torch.float32, device=x.device)
+    lib = _lib.library()
+    _lib.check(lib.gesso_moe_pair_up(_p(x), _dt(x), _p(w_up), _dt(w_up), _p(idx), _p(a), N, top, K, F, MOE_ACTS[act],
+                                     _stream()), "moe_pair_up")
+    _lib.check(lib.gesso_moe_pair_down(_p(a), _dt(a), _p(w_down), _dt(w_down), _p(idx), _p(w), _p(y), N, top, F, Hout,
+                                       _stream()), "moe_pair_down")
+    return y
+
+
+def moe_grouped_takes(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, top: int) -> bool:
+    """Whether the grouped tensor-core path takes this step (see :func:`moe_experts_grouped`)."""
+    return False
+
+
 # ---- short convolution -----------------------------------------------------------------------
 def short_conv(bcx: torch.Tensor, in_bias: Optional[torch.Tensor], taps: torch.Tensor,
                conv_bias: Optional[torch.Tensor], state: torch.Tensor, seg_of_token: torch.Tensor,
@@ -196,22 +304,31 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Opti
                        positions: torch.Tensor, seg_of_token: torch.Tensor, block_table: torch.Tensor,
                        k_pages: torch.Tensor, v_pages: torch.Tensor, nh: int, nkv: int, hd: int,
                        write_kv: bool, status: torch.Tensor, tiles=None, rot_dim: Optional[int] = None,
-                       interleaved: bool = False) -> torch.Tensor:
+                       interleaved: bool = False, bias: Optional[torch.Tensor] = None,
+                       v_head_dim: Optional[int] = None) -> torch.Tensor:
     """Norm + rotate q and k, write k and v into their pages; returns q as [N, nh, hd].  ``tiles`` =
     (seg_start, seg_pos0, tile_seg, tile_q0) of a step with prompt portions lets bfloat16 runs take the
     kernel that works by 64-token tiles (wide loads, v written along the slots of its transposed page).
     ``rot_dim`` (default: the head size) is how many leading features of a head the tables rotate, the
-    rest pass through normed; ``interleaved`` pairs neighbours (2i, 2i+1) instead of the two halves."""
+    rest pass through normed; ``interleaved`` pairs neighbours (2i, 2i+1) instead of the two halves.
+    ``bias``: float32 along the fused row, added before norm and rotation (and to v).  ``v_head_dim``: the
+    width of a value head where it differs from ``hd``.  The row may carry further columns behind the v
+    heads (an output gate's, say); they are left alone."""
     _cuda_contig(qkv, "qkv")
     N = qkv.shape[0]
-    heads = nh + 2 * nkv if write_kv else nh
-    _need(qkv.shape[1] == heads * hd, "fused projection width differs from the head layout")
+    vd = hd if v_head_dim is None else int(v_head_dim)
+    width = (nh + nkv) * hd + nkv * vd if write_kv else nh * hd
+    plain = qkv.shape[1] == width and vd == hd and bias is None
+    _need(qkv.shape[1] >= width, "fused projection width differs from the head layout")
+    if bias is not None:
+        _cuda_contig(bias, "bias", torch.float32)
+        _need(bias.numel() >= width, "projection bias is shorter than the fused row")
     _need(k_pages.dtype == qkv.dtype and v_pages.dtype == qkv.dtype, "cache pages must have the run dtype")
     _need(k_pages.is_contiguous() and v_pages.is_contiguous(), "cache pages must be contiguous")
     _need(k_pages.dim() == 4 and k_pages.shape[1] == nkv and k_pages.shape[3] == hd,
           "K pages must be [pages, kv heads, page size, head size]")
-    _need(tuple(v_pages.shape) == (k_pages.shape[0], nkv, hd, k_pages.shape[2]),
-          "V pages must be [pages, kv heads, head size, page size]")
+    _need(tuple(v_pages.shape) == (k_pages.shape[0], nkv, vd, k_pages.shape[2]),
+          "V pages must be [pages, kv heads, value size, page size]")
     page_size = k_pages.shape[2]
     _cuda_contig(block_table, "block_table", torch.int32)
     _cuda_contig(positions, "positions", torch.int32)
@@ -226,7 +343,7 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Opti
         rot_dim = 0
     q_out = torch.empty((N, nh, hd), dtype=qkv.dtype, device=qkv.device)
     full_half_split = cos is None or (rot_dim == hd and not interleaved)
-    if (tiles is not None and write_kv and qkv.dtype == torch.bfloat16 and tiles[2].numel() > 0 and full_half_split
+    if (tiles is not None and plain and write_kv and qkv.dtype == torch.bfloat16 and tiles[2].numel() > 0 and full_half_split
             and _lib.library().gesso_qk_rope_store_tiles_takes(hd, page_size, nh, nkv)):
         seg_start, seg_pos0, tile_seg, tile_q0 = tiles
         _lib.check(_lib.library().gesso_qk_norm_rope_store_tiles(
@@ -238,23 +355,38 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Opti
         _p(qkv), _dt(qkv), _p(q_w), _p(k_w), float(eps), _p(cos), _p(sin), _p(positions),
         _p(seg_of_token), _p(block_table), block_table.shape[1], page_size, _p(q_out), _p(k_pages),
         _p(v_pages), N, nh, nkv, hd, 1 if write_kv else 0, int(rot_dim), 1 if interleaved else 0, _p(status),
-        _stream()), "qk_norm_rope_store")
+        _p(bias), int(qkv.shape[1]), vd, _stream()), "qk_norm_rope_store")
     return q_out
 
 
 def paged_attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                             block_table: torch.Tensor, positions: torch.Tensor,
-                            seg_of_token: torch.Tensor, window: Optional[int], scale: float) -> torch.Tensor:
+                            seg_of_token: torch.Tensor, window: Optional[int], scale: float,
+                            keep_first: int = 0, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """FP32-arithmetic attention over the pages.  ``keep_first``: with a window, the first positions of the
+    sequence that stay visible.  ``gate``: a 2-D view ``[N, nh * value size]`` with unit column stride (columns of
+    the fused projection, say) whose sigmoid multiplies the result."""
     _cuda_contig(q, "q")
     N, nh, hd = q.shape
     nkv, page_size = k_pages.shape[1], k_pages.shape[2]
+    vd = v_pages.shape[2]
     _need(k_pages.dtype == q.dtype, "cache pages must have the dtype of q")
-    out = torch.empty((N, nh * hd), dtype=q.dtype, device=q.device)
+    out = torch.empty((N, nh * vd), dtype=q.dtype, device=q.device)
+    gate_stride = _check_gate(gate, N, nh * vd, q.dtype)
     _lib.check(_lib.library().gesso_paged_attention_generic(
         _p(q), _p(k_pages), _p(v_pages), _dt(q), _p(block_table), block_table.shape[1], page_size,
         _p(positions), _p(seg_of_token), _p(out), N, nh, nkv, hd, int(window or 0), float(scale),
-        _stream()), "paged_attention_generic")
+        vd, int(keep_first or 0), _p(gate), gate_stride, _stream()), "paged_attention_generic")
     return out
+
+
+def _check_gate(gate: Optional[torch.Tensor], n: int, width: int, dtype) -> int:
+    """Row stride of an output gate given as a view into a wider row-major tensor (0 without a gate)."""
+    if gate is None:
+        return 0
+    _need(gate.is_cuda and gate.dim() == 2 and tuple(gate.shape) == (n, width) and gate.stride(1) == 1
+          and gate.dtype == dtype, "gate must be [tokens, heads * value size] of the run dtype with unit column stride")
+    return int(gate.stride(0))
 
 
 # ---- feed-forward ------------------------------------------------------------------------------

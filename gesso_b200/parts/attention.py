@@ -10,6 +10,18 @@ Scores are ``q.k / sqrt(head_dim)`` (:1201-1205), causal, optionally limited to 
 Parameters (all from the part spec): hidden_size, n_heads, n_kv_heads, head_dim,
 qk_norm_eps (``None``: no q/k norm), window (``None``: all keys), position (a position
 part spec).  The three projections are fused into one matrix at bind time.
+
+Options, all off by default, each a parameter so that any architecture can turn it on:
+``v_head_dim`` (values of another width than queries and keys; the output projection then reads
+``n_heads * v_head_dim`` features); ``qkv_bias`` (bias vectors ``q_proj.bias``, ``k_proj.bias``,
+``v_proj.bias``, added in the projection, before rotation); ``scale`` (the score scale, instead of
+``1/sqrt(head_dim)``); ``keep_first`` (with a window: position i sees j if ``j <= i`` and
+``(i - j < window or j < keep_first)``; the kept tokens keep their true positions for the rotation,
+and the cache manager keeps their pages); ``output_gate`` (a fourth projection ``g_proj`` of the
+mixer's input, ``n_heads * v_head_dim`` wide: the concatenated heads are multiplied element by
+element with ``sigmoid(g)`` before the output projection; it rides in the fused matrix and the
+attention kernels apply it as they store); ``f32_output`` (the output projection's result in
+float32, for arrangements that norm it before the add).
 """
 from __future__ import annotations
 
@@ -36,6 +48,15 @@ class GQAttention(Mixer):
         self.hd = int(spec["head_dim"])
         self.eps = spec.get("qk_norm_eps")
         self.window = spec.get("window")
+        self.vd = int(spec.get("v_head_dim") or self.hd)
+        self.qkv_bias = bool(spec.get("qkv_bias", False))
+        self.output_gate = bool(spec.get("output_gate", False))
+        self.keep_first = int(spec.get("keep_first") or 0)
+        self.f32_output = bool(spec.get("f32_output", False))
+        if self.vd < 1 or self.vd > 256:
+            raise invalid(f"attention: v_head_dim {self.vd} must be between 1 and 256")
+        if self.keep_first < 0:
+            raise invalid("attention: keep_first must be >= 0")
         if self.nh < 1 or self.nkv < 1 or self.nh % self.nkv != 0:
             raise invalid(f"attention: {self.nh} heads are not a multiple of {self.nkv} kv heads")
         if self.hd < 2 or self.hd % 2 != 0 or self.hd > 256:
@@ -46,29 +67,45 @@ class GQAttention(Mixer):
         self.position.check_head_dim(self.hd)
         # 1/sqrt(hd) rounded once from float64 (exact when sqrt(hd) is a power of two,
         # src/Inference/Inference.jl:1209-1232)
-        self.scale = 1.0 / math.sqrt(self.hd)
+        self.scale = 1.0 / math.sqrt(self.hd) if spec.get("scale") is None else float(spec["scale"])
 
     def param_decls(self) -> Dict[str, ParamDecl]:
-        q, kv = self.nh * self.hd, self.nkv * self.hd
+        q, kv, v, o = self.nh * self.hd, self.nkv * self.hd, self.nkv * self.vd, self.nh * self.vd
         d = {
             "q_proj.weight": ParamDecl((q, self.hidden), fan_in=self.hidden),
             "k_proj.weight": ParamDecl((kv, self.hidden), fan_in=self.hidden),
-            "v_proj.weight": ParamDecl((kv, self.hidden), fan_in=self.hidden),
-            "o_proj.weight": ParamDecl((self.hidden, q), fan_in=q),
+            "v_proj.weight": ParamDecl((v, self.hidden), fan_in=self.hidden),
+            "o_proj.weight": ParamDecl((self.hidden, o), fan_in=o),
         }
+        if self.qkv_bias:
+            d["q_proj.bias"] = ParamDecl((q,), role="vector", init="zeros")
+            d["k_proj.bias"] = ParamDecl((kv,), role="vector", init="zeros")
+            d["v_proj.bias"] = ParamDecl((v,), role="vector", init="zeros")
+        if self.output_gate:
+            d["g_proj.weight"] = ParamDecl((o, self.hidden), fan_in=self.hidden)
         if self.eps is not None:
             d["q_norm.weight"] = ParamDecl((self.hd,), role="vector", init="ones")
             d["k_norm.weight"] = ParamDecl((self.hd,), role="vector", init="ones")
         return d
 
     def cache_need(self):
-        return PagedNeed(self.nkv, self.hd, None if self.window is None else int(self.window))
+        windowed = self.window is not None
+        return PagedNeed(self.nkv, self.hd, int(self.window) if windowed else None,
+                         self.keep_first if windowed else 0, None if self.vd == self.hd else self.vd)
 
     def bind(self, tensors, rt) -> None:
         ws = [tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]]
-        common = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
-        self.w_q = ws[0].to(common).contiguous()
-        self.w_qkv = torch.cat([w.to(common) for w in ws], dim=0).contiguous()
+        gate = [tensors["g_proj.weight"]] if self.output_gate else []
+        common = torch.float32 if any(w.dtype == torch.float32 for w in ws + gate) else ws[0].dtype
+        # the fused rows: q heads, k heads, v heads, then the gate's columns; an entry that reads another
+        # entry's cache projects q (and the gate) only
+        self.w_q = torch.cat([w.to(common) for w in ws[:1] + gate], dim=0).contiguous()
+        self.w_qkv = torch.cat([w.to(common) for w in ws + gate], dim=0).contiguous()
+        self.b_q = self.b_qkv = None
+        if self.qkv_bias:
+            bs = [tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"]]
+            self.b_q = bs[0].float().contiguous()
+            self.b_qkv = torch.cat([b.float() for b in bs]).contiguous()
         self.w_o = tensors["o_proj.weight"]
         self.q_norm = tensors.get("q_norm.weight")
         self.k_norm = tensors.get("k_norm.weight")
@@ -91,11 +128,16 @@ class GQAttention(Mixer):
                                    cache.k_pages, cache.v_pages, self.nh, self.nkv, self.hd, writes, ctx.status,
                                    tiles=None if ctx.decode_only else (ctx.seg_start, ctx.seg_pos0, ctx.tile_seg,
                                                                        ctx.tile_q0),
-                                   rot_dim=rot_dim or None, interleaved=interleaved)
-        o = self.rt.attention(q, cache, ctx, self.window, self.scale)
+                                   rot_dim=rot_dim or None, interleaved=interleaved,
+                                   bias=self.b_qkv if writes else self.b_q, v_head_dim=self.vd)
+        gate = None
+        if self.output_gate:          # the gate's columns of the fused projection, behind q (, k and v)
+            g0 = (self.nh + self.nkv) * self.hd + self.nkv * self.vd if writes else self.nh * self.hd
+            gate = qkv[:, g0:g0 + self.nh * self.vd]
+        o = self.rt.attention(q, cache, ctx, self.window, self.scale, keep_first=self.keep_first, gate=gate)
         if residual is not None:
             return ops.linear_residual(o, self.w_o, residual, None), None
-        return ops.linear(o, self.w_o, out_dtype=x.dtype), None
+        return ops.linear(o, self.w_o, out_dtype=torch.float32 if self.f32_output else x.dtype), None
 
 
 register_mixer("gqa_attention", GQAttention, replace=True)

@@ -51,12 +51,20 @@ class PagedNeed:
 
     ``window`` is ``None`` when every earlier key is read, or the number of most
     recent positions (the current one included) that a query reads; pages wholly
-    behind the window are given back.
+    behind the window are given back, except those that hold one of the first
+    ``keep_first`` positions of the sequence, which a windowed query keeps reading.
+    ``v_head_dim`` is the width of a value head where it differs from ``head_dim``.
     """
 
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    keep_first: int = 0
+    v_head_dim: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)

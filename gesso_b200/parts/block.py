@@ -9,11 +9,15 @@ The residual stream ``h`` is float32 and is updated in place.  A sublayer's outp
 added at once: it travels as ``pending = (delta, bias)`` to the next norm, which adds it into
 ``h`` and norms the sum in one kernel (the reference fuses the same add+norm on its decode
 path, src/Inference/Inference.jl:3239-3247).
+
+``sandwich``: each sublayer's output is normed once more before it is added (see :class:`SandwichBlock`).
 """
 from __future__ import annotations
 
 from typing import Dict
 
+from .. import ops
+from ..errors import invalid
 from .base import ParamDecl
 from .registry import (build_feed_forward, build_mixer, build_norm, register_block)
 
@@ -74,4 +78,65 @@ class PreNormBlock:
         return norm.add_norm(h, pending[0], pending[1])
 
 
+class SandwichBlock:
+    """Norm before AND after each sublayer::
+
+        h = h + PostNorm_m( Mixer(Norm_m(h)) )
+        h = h + PostNorm_f( FeedForward(Norm_f(h)) )        (left out when the layer has no feed-forward)
+
+    A sublayer's output travels on as ``pending = (PostNormed(delta, post norm), None)``: the next pre norm
+    norms it, adds it into the float32 stream and norms the sum in one kernel.  The post norms must be
+    Dynamic Tanh norms (the fused kernel's form); the pre norms may be any registered norm."""
+
+    def __init__(self, block_spec):
+        self.spec = block_spec
+        if block_spec.mixer_post_norm is None:
+            raise invalid("sandwich block: needs a mixer_post_norm")
+        self.mixer = build_mixer(block_spec.mixer)
+        self.mixer_norm = build_norm(block_spec.mixer_norm)
+        self.mixer_post_norm = build_norm(block_spec.mixer_post_norm)
+        self.feed_forward = self.ff_norm = self.ff_post_norm = None
+        if block_spec.feed_forward is not None:
+            if block_spec.ff_norm is None or block_spec.ff_post_norm is None:
+                raise invalid("sandwich block: a feed-forward needs ff_norm and ff_post_norm")
+            self.feed_forward = build_feed_forward(block_spec.feed_forward)
+            self.ff_norm = build_norm(block_spec.ff_norm)
+            self.ff_post_norm = build_norm(block_spec.ff_post_norm)
+        for n in (self.mixer_post_norm, self.ff_post_norm):
+            if n is not None and not hasattr(n, "params"):
+                raise invalid("sandwich block: post norms must be of a kind that fuses with the residual add (dyt)")
+
+    def parts(self):
+        out = [("mixer_norm.", self.mixer_norm), ("mixer.", self.mixer), ("mixer_post_norm.", self.mixer_post_norm)]
+        if self.feed_forward is not None:
+            out += [("ff_norm.", self.ff_norm), ("feed_forward.", self.feed_forward),
+                    ("ff_post_norm.", self.ff_post_norm)]
+        return tuple(out)
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        out = {}
+        for prefix, part in self.parts():
+            for name, decl in part.param_decls().items():
+                out[prefix + name] = decl
+        return out
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def bind(self, tensors, rt) -> None:
+        for prefix, part in self.parts():
+            part.bind({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}, rt)
+
+    def forward(self, h, pending, ctx, cache):
+        x = self.mixer_norm.add_norm(h, pending[0], pending[1])
+        d, b = self.mixer.forward(x, ctx, cache)
+        pending = (ops.PostNormed(d, self.mixer_post_norm.params(), b), None)
+        if self.feed_forward is None:
+            return pending
+        x = self.ff_norm.add_norm(h, pending[0], None)
+        d, b = self.feed_forward.forward(x, ctx)
+        return ops.PostNormed(d, self.ff_post_norm.params(), b), None
+
+
 register_block("prenorm", PreNormBlock, replace=True)
+register_block("sandwich", SandwichBlock, replace=True)

@@ -48,10 +48,53 @@ class RMSNorm(Norm):
         return self.folded
 
     def add_norm(self, h, delta, delta_bias, rows=None, lazy=False):
+        if isinstance(delta, ops.PostNormed):      # a sublayer's output that is normed before the add
+            if rows is not None:
+                raise NotImplementedError("rmsnorm: a post-normed delta cannot be added for a row list")
+            delta.add_into(h)
+            delta = None
         weight = None if self.folded else self.weight
         if lazy and delta is None and rows is None:
             return ops.LazyNorm(h, weight, self.eps, self.out_dtype)
         return ops.add_rmsnorm(h, delta, delta_bias, weight, self.eps, self.out_dtype, rows)
 
 
+class DynamicTanh(Norm):
+    """Dynamic Tanh: ``y = tanh(alpha * x) * weight + bias`` with a learned scalar ``alpha``; no mean, no
+    variance, no eps.  Parameters: ``size``, ``bias`` (default true).  Tensors: ``weight`` [size], ``bias``
+    [size], ``alpha`` [] (read once at bind time).
+
+    ``add_norm`` adds the pending delta into the float32 stream and norms the sum in one kernel; a pending
+    :class:`~gesso_b200.ops.PostNormed` (a sublayer's output that is itself normed before the add) is handled
+    in the same pass.  ``params()`` hands the norm to such a caller."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.size = int(spec["size"])
+        self.has_bias = bool(spec.get("bias", True))
+        self.p = None
+        self.out_dtype = None
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        d = {"weight": ParamDecl((self.size,), role="vector", init="ones"),
+             "alpha": ParamDecl((), role="vector", init="ones", alt_shapes=((1,),))}
+        if self.has_bias:
+            d["bias"] = ParamDecl((self.size,), role="vector", init="zeros")
+        return d
+
+    def bind(self, tensors, rt) -> None:
+        self.p = ops.DytParams(float(tensors["alpha"].reshape(-1)[0].item()), tensors["weight"], tensors.get("bias"))
+        self.out_dtype = rt.dtype
+
+    def params(self) -> "ops.DytParams":
+        return self.p
+
+    def add_norm(self, h, delta, delta_bias, rows=None):
+        post = None
+        if isinstance(delta, ops.PostNormed):
+            delta, post, delta_bias = delta.delta, delta.post, delta.bias
+        return ops.add_dyt(h, delta, delta_bias, post, self.p, self.out_dtype, rows)
+
+
 register_norm("rmsnorm", RMSNorm, replace=True)
+register_norm("dyt", DynamicTanh, replace=True)

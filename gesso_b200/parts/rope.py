@@ -11,7 +11,8 @@ Parameters: ``theta``; ``rotary_dim`` (even, at most the head size: the leading
 ``rotary_dim`` features of a head are rotated with ``d = rotary_dim``, the rest are
 left alone; LFM2 rotates the whole head, and its configuration reader refuses
 anything else as the reference does, src/Inference/lfm2.jl:66-70); ``interleaved``
-(pairs ``(2i, 2i+1)`` instead of the halves; default false).  A position part hands
+(pairs ``(2i, 2i+1)`` instead of the halves; default false); ``scaling_factor`` (linear
+scaling: every frequency is divided by it; default 1).  A position part hands
 the attention part ``tables()`` = (cos, sin) and ``layout()`` = (rotary size,
 interleaved).
 """
@@ -24,10 +25,11 @@ from .base import Position
 from .registry import register_position
 
 
-def rope_tables(theta: float, dim: int, max_positions: int):
-    """(cos, sin) float32 CPU tensors ``[max_positions, dim/2]`` from float64 angles."""
+def rope_tables(theta: float, dim: int, max_positions: int, scaling_factor: float = 1.0):
+    """(cos, sin) float32 CPU tensors ``[max_positions, dim/2]`` from float64 angles; with linear scaling
+    every frequency is divided by ``scaling_factor``."""
     i = torch.arange(dim // 2, dtype=torch.float64)
-    inv_freq = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * i / dim)
+    inv_freq = torch.pow(torch.tensor(float(theta), dtype=torch.float64), -2.0 * i / dim) / float(scaling_factor)
     ang = torch.arange(max_positions, dtype=torch.float64)[:, None] * inv_freq[None, :]
     return torch.cos(ang).to(torch.float32), torch.sin(ang).to(torch.float32)
 
@@ -38,6 +40,9 @@ class RotaryPosition(Position):
         self.theta = float(spec["theta"])
         self.rotary_dim = int(spec["rotary_dim"])
         self.interleaved = bool(spec.get("interleaved", False))
+        self.scaling_factor = float(spec.get("scaling_factor", 1.0) or 1.0)     # linear scaling of the positions
+        if not self.scaling_factor > 0:
+            raise invalid("rope: scaling_factor must be positive")
         if self.rotary_dim % 2 != 0 or self.rotary_dim < 2:
             raise invalid("rope: rotary_dim must be even and at least 2")
         self.cos = self.sin = None
@@ -51,9 +56,9 @@ class RotaryPosition(Position):
         return self.rotary_dim, self.interleaved
 
     def bind(self, tensors, rt) -> None:
-        key = ("rope", self.theta, self.rotary_dim)
+        key = ("rope", self.theta, self.rotary_dim, self.scaling_factor)
         if key not in rt.shared:
-            cos, sin = rope_tables(self.theta, self.rotary_dim, rt.max_positions)
+            cos, sin = rope_tables(self.theta, self.rotary_dim, rt.max_positions, self.scaling_factor)
             rt.shared[key] = (cos.to(rt.device).contiguous(), sin.to(rt.device).contiguous())
         self.cos, self.sin = rt.shared[key]
 
