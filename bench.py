@@ -40,6 +40,9 @@ both through ``Session.run_batch`` (scheduler, cache manager, sampler), with the
 a step;
 
     python bench.py --workload timeline --batch 8      # the kernels of one decoding step, by name
+    python bench.py --workload sodurax       # Sodurax layers (gated windowed attention, routed experts, Dynamic
+                                             # Tanh norms) at three sizes beside all-attention LFM2 layers of equal
+                                             # size: prefill and decode throughput, and both models' kernels by name
 
 a table (not JSON) of where a step's time goes, from the CUPTI activity trace.
 
@@ -460,6 +463,138 @@ def kernel_timeline(batch: int, context: int, page_size: int, layers=None) -> in
     return 0
 
 
+# ---- Sodurax beside LFM2 at equal size -----------------------------------------------------------------------
+# name -> width, heads, kv heads, head size, experts, expert width, experts per token, groups, groups kept, window,
+# kept first tokens, rotated features.  The LFM2 model beside it has attention layers only, the same width and
+# heads, and a dense feed-forward as wide as the experts one token uses (top * expert width).
+SODURAX_SIZES = {
+    "w1024": dict(width=1024, heads=16, kv=4, dim=64, experts=16, ff=512, top=4, groups=4, keep=2, window=1024, first=4, rot=32),
+    "w2048": dict(width=2048, heads=32, kv=8, dim=64, experts=32, ff=1024, top=4, groups=8, keep=4, window=2048, first=4, rot=32),
+    "w2048h128": dict(width=2048, heads=16, kv=4, dim=128, experts=64, ff=768, top=6, groups=8, keep=4, window=1024, first=16, rot=64),
+}
+SODURAX_LAYERS = 4
+SODURAX_VOCAB = 32768
+
+
+def sodurax_configs(z):
+    mixer = {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+             "rot": {"base": 1e6, "dims": z["rot"], "scaling": {"factor": 4.0}},
+             "mask": {"size": z["window"], "keep_first": z["first"]}}
+    mlp = {"kind": "moe", "expert": {"ff": z["ff"]},
+           "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": z["groups"], "keep": z["keep"]}}}
+    sdx = {"architecture": "Sodurax", "vocab": SODURAX_VOCAB, "width": z["width"], "norm": {"eps": 1e-6},
+           "layers": [{"type": "attention", "mixer": mixer, "mlp": mlp} for _ in range(SODURAX_LAYERS)]}
+    lfm = dict(LFM2_1_2B, vocab_size=SODURAX_VOCAB, hidden_size=z["width"], num_hidden_layers=SODURAX_LAYERS,
+               num_attention_heads=z["heads"], num_key_value_heads=z["kv"], head_dim=z["dim"],
+               full_attn_idxs=list(range(SODURAX_LAYERS)), block_ff_dim=z["top"] * z["ff"], block_auto_adjust_ff_dim=False)
+    return sdx, lfm
+
+
+def kernels_by_name(run, n=2):
+    """The kernels of ``n`` calls of ``run`` by kernel name (CUPTI through torch.profiler), in us per call: the time
+    from a kernel's start to the start of the next one (kernels launched programmatically start while their
+    predecessor drains and wait inside, so their own durations overlap and add up to more than the step; the
+    starts do not), and the number of launches."""
+    import collections
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(n):
+            run()
+        torch.cuda.synchronize()
+    ev = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA
+          and "Memcpy" not in e.name and "Memset" not in e.name]
+    ev.sort(key=lambda e: e.time_range.start)
+    agg = collections.OrderedDict()
+    for i, e in enumerate(ev):
+        nxt = ev[i + 1].time_range.start if i + 1 < len(ev) else e.time_range.end
+        a = agg.setdefault(e.name.split("(")[0].split("<")[0][-56:], [0.0, 0])
+        a[0] += min(nxt, e.time_range.end + 50.0) - e.time_range.start     # a gap between two calls is nobody's time
+        a[1] += 1
+    return {k: [round(v[0] / n, 1), v[1] // n] for k, v in sorted(agg.items(), key=lambda kv: -kv[1][0])}
+
+
+def sodurax_workload(args) -> int:
+    import torch
+    import gesso_b200 as gb
+    from gesso_b200.engine.batch import StepEntry
+    from gesso_b200.engine.engine import Engine
+    from gesso_b200 import ops
+    pk = peaks()
+    warmup = max(args.warmup, 3)
+    steps = min(args.steps, 64)
+    sampler = ClockSampler(device_uuid())
+    sampler.start()
+    out = {}
+    for name, z in SODURAX_SIZES.items():
+        if args.sizes and name not in args.sizes.split(","):
+            continue
+        row = {}
+        for which, cfg in zip(("sodurax", "lfm2"), sodurax_configs(z)):
+            model = gb.random_model(cfg, seed=0, dtype="bfloat16", max_positions=args.context, style="fan_in")
+            ms_pre = time_prefill(gb, model, args.prefill_tokens, args.page_size)
+            ms_dec, launches, kv_mid = time_decode(gb, model, args.batch, args.context, steps, warmup, args.page_size)
+            # bytes of a decoding step: the matrices it reads once (for the experts: those that batch * top pairs
+            # touch, at most all) and the keys and values a query reads; flops of a prefill step: the matrices a
+            # token uses and the causal (windowed) attention
+            W, H, G, D = z["width"], z["heads"], z["kv"], z["dim"]
+            attn_w = W * (H * D + 2 * G * D) + H * D * W + (H * D * W if which == "sodurax" else 0)
+            if which == "sodurax":
+                touched = min(z["experts"], args.batch * z["top"])
+                ff_w_decode = touched * 2 * z["ff"] * W + z["experts"] * W
+                ff_w_token = z["top"] * 2 * z["ff"] * W + z["experts"] * W
+                keys = min(kv_mid, z["window"] + z["first"])
+                keys_prefill = min(args.prefill_tokens / 2, z["window"])
+            else:
+                ff_w_decode = ff_w_token = 3 * z["top"] * z["ff"] * W
+                keys, keys_prefill = kv_mid, args.prefill_tokens / 2
+            head = SODURAX_VOCAB * W
+            dec_bytes = 2 * (SODURAX_LAYERS * (attn_w + ff_w_decode) + head) + args.batch * keys * SODURAX_LAYERS * 2 * G * D * 2
+            pre_flops = args.prefill_tokens * 2 * (SODURAX_LAYERS * (attn_w + ff_w_token + 2 * keys_prefill * H * D))
+            row[which] = {
+                "prefill_ms": round(ms_pre, 4), "prefill_tok_s": round(args.prefill_tokens * 1000 / ms_pre, 1),
+                "prefill_frac_of_bf16_peak": round(pre_flops / (ms_pre * 1e-3) / 1e12 / pk["bf16_tflops"], 4),
+                "decode_ms_per_step": round(ms_dec, 4), "decode_tok_s": round(args.batch * 1000 / ms_dec, 1),
+                "decode_frac_of_hbm_peak": round(dec_bytes / (ms_dec * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
+                "gpu_launches_per_decode_step": launches // steps}
+            if args.kernels:
+                eng = Engine(model, max_positions=args.context, page_size=args.page_size,
+                             num_pages=(args.batch + 1) * (args.context // args.page_size + 1), max_requests=args.batch + 1)
+                g = torch.Generator().manual_seed(5)
+                prompt = torch.randint(0, model.vocab_size, (args.prefill_tokens,), generator=g).tolist()
+                for i in range(args.batch):
+                    eng.admit(i)
+                    eng.step([StepEntry(i, prompt, [])])
+                n_pre = [0]
+
+                def pre():
+                    rid = f"p{n_pre[0]}"
+                    n_pre[0] += 1
+                    eng.admit(rid)
+                    eng.step([StepEntry(rid, prompt, [args.prefill_tokens - 1])])
+                    eng.release(rid)
+
+                def dec():
+                    ops.argmax_rows(eng.step([StepEntry(i, [7 + i], [0]) for i in range(args.batch)]))
+                for _ in range(3):                  # the steps' graphs are captured
+                    pre(), dec()
+                row[which]["prefill_kernels_us"] = kernels_by_name(pre)
+                row[which]["decode_kernels_us"] = kernels_by_name(dec)
+                eng.check_status()
+            del model
+            torch.cuda.empty_cache()
+        row["prefill_ratio"] = round(row["sodurax"]["prefill_tok_s"] / row["lfm2"]["prefill_tok_s"], 3)
+        row["decode_ratio"] = round(row["sodurax"]["decode_tok_s"] / row["lfm2"]["decode_tok_s"], 3)
+        out[name] = dict(row, sizes=z)
+    print(json.dumps({
+        "workload": "sodurax", "metric": "prefill and decode tokens/s of Sodurax layers beside LFM2 attention layers of equal size",
+        "unit": "tokens/s", "layers": SODURAX_LAYERS, "vocab": SODURAX_VOCAB, "batch": args.batch, "context": args.context,
+        "prefill_tokens": args.prefill_tokens, "dtype": "bf16", "data": "synthetic (uniform-random token ids, random weights seed 0)",
+        "peaks": pk, "sizes": out, "clocks": sampler.summary()}))
+    return 0
+
+
 def reference_arm():
     """The reference is a Julia 1.12 project (Project.toml, no setup.py / pyproject.toml): pip cannot
     install it, no Julia toolchain exists here, and its CUDA extension has no short-convolution
@@ -482,9 +617,12 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
-    ap.add_argument("--workload", default="decode", choices=["decode", "timeline"] + sorted(SERVE),
+    ap.add_argument("--workload", default="decode", choices=["decode", "timeline", "sodurax"] + sorted(SERVE),
                     help="decode: the headline (default); serve350m / serve700m: serving-like runs through run_batch; "
-                         "timeline: the kernels of one decoding step at --batch and --context")
+                         "timeline: the kernels of one decoding step at --batch and --context; sodurax: Sodurax layers "
+                         "beside LFM2 attention layers of equal size")
+    ap.add_argument("--sizes", default="", help="sodurax workload: which of its sizes to run, with commas (default: all)")
+    ap.add_argument("--kernels", action="store_true", help="sodurax workload: also the kernels of a step by name")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -493,6 +631,8 @@ def main() -> int:
         return 2
     if args.workload == "timeline":
         return kernel_timeline(args.batch, args.context, args.page_size, args.layers)
+    if args.workload == "sodurax":
+        return sodurax_workload(args)
     if args.workload != "decode":
         return serve_workload(args.workload)
     warmup = max(args.warmup, 3)

@@ -1,5 +1,5 @@
-"""gesso_b200: a small, whole LFM2 inference engine for one NVIDIA B200."""
-from . import config as _config  # noqa: F401  (registers the built-in architecture)
+"""gesso_b200: a small, whole inference engine (LFM2 and Sodurax models) for one NVIDIA B200."""
+from . import config as _config  # noqa: F401  (registers the built-in architectures)
 from . import parts as _parts    # noqa: F401  (registers the built-in parts)
 from .api import load, random_model, run_dtype
 from .errors import ErrorCode, GessoError

@@ -205,7 +205,8 @@ class SoduraxConfig:
         return PartSpec("gqa_attention", {
             "hidden_size": self.width, "n_heads": a.heads, "n_kv_heads": a.kv_heads, "head_dim": a.dim,
             "v_head_dim": a.vdim, "qk_norm_eps": None, "window": a.window, "keep_first": a.keep_first,
-            "scale": a.scale, "qkv_bias": True, "output_gate": True, "f32_output": True, "position": position})
+            "scale": a.scale, "qkv_bias": True, "output_gate": True, "f32_output": True, "f32_weights": True,
+            "position": position})
 
     def _mlp_spec(self, m: SoduraxMoE) -> PartSpec:
         return PartSpec("routed_experts", {

@@ -89,11 +89,14 @@ __device__ __forceinline__ void load_block(KVFrag<HD>& f, const bf16* __restrict
 // and g+8; lo_a / lo_b: first visible key.  key0: first key of the block.
 // UPPER = false: rows 8..15 of the tile carry no query (a decoding step with at most 8 query heads per kv
 // head): their scores are not looked at, their probabilities are zero and their outputs are never read.
-template <int HD, bool UPPER = true>
+// keep: with a window, keys below `keep` stay visible (0: none).  PSPLIT: a probability enters the P V product
+// as the sum of two bfloat16 numbers (its rounding and the rounding of what is left), i.e. with 16 bits of
+// mantissa instead of 8, for mixers whose attention weights are to act in 32-bit precision.
+template <int HD, bool UPPER = true, bool PSPLIT = false>
 __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&qf)[HD / 32],
                                              const uint4 (&qg)[HD / 32], float (&o)[HD / 8][4], float (&m)[2],
                                              float (&l)[2], int key0, int t, int pos_a, int pos_b, int lo_a,
-                                             int lo_b, float scale_log2, bool need_mask) {
+                                             int lo_b, float scale_log2, bool need_mask, int keep = 0) {
     float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int c = 0; c < HD / 32; ++c) {
@@ -112,8 +115,8 @@ __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&
         if (UPPER) sb[i] *= scale_log2;
         if (need_mask) {
             const int key = kbase + i;
-            if (key > pos_a || key < lo_a) sa[i] = -INFINITY;
-            if (UPPER && (key > pos_b || key < lo_b)) sb[i] = -INFINITY;
+            if (key > pos_a || (key < lo_a && key >= keep)) sa[i] = -INFINITY;
+            if (UPPER && (key > pos_b || (key < lo_b && key >= keep))) sb[i] = -INFINITY;
         }
     }
     // The running maximum is kept as a whole number (scores are in the base-2 domain): rescaling by
@@ -149,6 +152,17 @@ __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&
     }
     const unsigned a0 = pack_bf16(pa[0], pa[1]), a1 = UPPER ? pack_bf16(pb[0], pb[1]) : 0u;
     const unsigned a2 = pack_bf16(pa[2], pa[3]), a3 = UPPER ? pack_bf16(pb[2], pb[3]) : 0u;
+    unsigned r0 = 0u, r1 = 0u, r2 = 0u, r3 = 0u;          // what the first rounding left of each probability
+    if (PSPLIT) {
+        float ra[4], rb[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            ra[i] = pa[i] - __bfloat162float(__float2bfloat16_rn(pa[i]));
+            rb[i] = pb[i] - __bfloat162float(__float2bfloat16_rn(pb[i]));
+        }
+        r0 = pack_bf16(ra[0], ra[1]); r2 = pack_bf16(ra[2], ra[3]);
+        if (UPPER) { r1 = pack_bf16(rb[0], rb[1]); r3 = pack_bf16(rb[2], rb[3]); }
+    }
     // the running maximum seldom moves after the first blocks: rescale only when some row's did
     const bool rescale = __any_sync(0xffffffffu, alpha_a != 1.f || alpha_b != 1.f);
 #pragma unroll
@@ -162,7 +176,13 @@ __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&
             }
         }
         mma_bf16(o[j], a0, a1, a2, a3, f.v[j].x, f.v[j].y);
+        if (PSPLIT) mma_bf16(o[j], r0, r1, r2, r3, f.v[j].x, f.v[j].y);
     }
+}
+
+// an output gate: the result times sigmoid(gate), gate rows `gate_stride` elements apart (null: no gate)
+__device__ __forceinline__ float gate_of(const bf16* __restrict__ gate, size_t at) {
+    return gate ? 1.f / (1.f + __expf(-__bfloat162float(gate[at]))) : 1.f;
 }
 
 // ================================ decode: split-KV ==============================================
@@ -200,14 +220,15 @@ __device__ __forceinline__ void cp_async_zfill8(void* smem_dst, const void* src,
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(d), "l"(src), "r"(valid ? 8 : 0));
 }
 
-template <int HD, int DA_STAGES, bool UPPER>
+template <int HD, int DA_STAGES, bool UPPER, bool PSPLIT>
 __global__ void __launch_bounds__(128)
 decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
                         const bf16* __restrict__ v_pages, const int* __restrict__ block_table, int max_pages,
                         int page_size, int page_shift, const int* __restrict__ positions,
                         bf16* __restrict__ out, int nh, int nkv, int window, float scale_log2, int n_splits,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ tickets,
-                        const int* __restrict__ kv_span, int slots) {
+                        const int* __restrict__ kv_span, int slots, int keep, const bf16* __restrict__ gate,
+                        int gate_stride) {
     // ring: [stage][piece][128 threads]: HD/16 pieces of 16 bytes for K, then HD/8 pieces of 8 bytes for V;
     // afterwards the same memory serves the merge of the warps ([4 warps][16 rows][HD + 2] floats)
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -224,7 +245,11 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     const int* bt = block_table + (size_t)seg * max_pages;
 
     const int first_block = lo / 16, last_block = pos / 16;
-    const int n_blocks = last_block - first_block + 1;
+    // With a window that keeps the first keys, the blocks of those keys come ahead of the window's: the warps
+    // walk a list of kb + (last_block - first_block + 1) blocks, `blk` turns a place in it into a key block.
+    const int kb = (window > 0 && keep > 0) ? min((keep + 15) / 16, first_block) : 0;
+    const int n_blocks = kb + last_block - first_block + 1;
+    auto blk = [&](int vb) { return vb < kb ? vb : first_block + (vb - kb); };
     int used = n_splits;                     // pieces this request is cut into
     if (n_splits > 1 && kv_span != nullptr) {
         const int n_segs = (int)gridDim.y;
@@ -249,8 +274,8 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
         return;
     }
     const int per = (n_blocks + used - 1) / used;
-    const int b0 = first_block + split * per;
-    const int b1 = min(last_block + 1, b0 + per);
+    const int b0 = split * per;                                       // places in the list of blocks
+    const int b1 = min(n_blocks, b0 + per);
     const int mine_n = b0 + w < b1 ? (b1 - b0 - w + 3) / 4 : 0;      // blocks b0 + w + 4 i of this warp
 
     // page ids of this warp's blocks, 32 at a time: lane i holds the page of block i of the batch
@@ -258,7 +283,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     int pages = 0;
     auto fetch_pages = [&](int first_i) {
         const int i = first_i + lane;
-        const int key = (b0 + w + 4 * i) * 16;
+        const int key = blk(b0 + w + 4 * i) * 16;
         pages = i < mine_n ? bt[page_shift >= 0 ? key >> page_shift : key / page_size] : -1;
     };
     fetch_pages(0);
@@ -275,7 +300,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     int issued = 0, issue_stage = 0;
     auto issue = [&]() {                     // request block `issued` of this warp into its ring stage
         if (issued < mine_n) {
-            const int key0 = (b0 + w + 4 * issued) * 16;
+            const int key0 = blk(b0 + w + 4 * issued) * 16;
             const int page = __shfl_sync(0xffffffffu, pages, issued & 31);
             const bool valid = page >= 0;    // a page given back behind a window: masked, zero-filled
             const int sub = page_shift >= 0 ? key0 & (page_size - 1) : key0 % page_size;
@@ -301,7 +326,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     int early = 0;
 #pragma unroll 1
     for (; early < DA_STAGES; ++early) {
-        if (issued < mine_n && b0 + w + 4 * issued == last_block) break;
+        if (issued < mine_n && blk(b0 + w + 4 * issued) == last_block) break;
         issue();
     }
     // let the successor in first (it only prefetches what no running kernel writes until its own wait)
@@ -328,7 +353,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     int read_stage = 0;
 #pragma unroll 1
     for (int i = 0; i < mine_n; ++i) {
-        const int b = b0 + w + 4 * i;
+        const int b = blk(b0 + w + 4 * i);
         asm volatile("cp.async.wait_group %0;\n" ::"n"(DA_STAGES - 1));
         const int stage_off = read_stage * STAGE_BYTES;
         if (++read_stage == DA_STAGES) read_stage = 0;
@@ -342,7 +367,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
         for (int j = 0; j < VP; ++j) cur.v[j] = *reinterpret_cast<const uint2*>(ring_mine_v + stage_off + j * 128 * 8);
         issue();                                          // refill the stage just read
         const bool need_mask = (b * 16 + 15 > pos) || (b * 16 < lo);
-        attend_block<HD, UPPER>(cur, qf, qg, o, m, l, b * 16, t, pos, pos, lo, lo, scale_log2, need_mask);
+        attend_block<HD, UPPER, PSPLIT>(cur, qf, qg, o, m, l, b * 16, t, pos, pos, lo, lo, scale_log2, need_mask, keep);
     }
     asm volatile("cp.async.wait_group 0;\n" ::);
     __syncthreads();                                      // the ring is free: it becomes the merge buffer
@@ -381,7 +406,8 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
         }
         const int head = kvh * G + r;
         if (used == 1) {
-            out[((size_t)tok * nh + head) * HD + d] = __float2bfloat16_rn(acc / L);
+            out[((size_t)tok * nh + head) * HD + d] =
+                __float2bfloat16_rn(acc / L * gate_of(gate, (size_t)tok * gate_stride + (size_t)head * HD + d));
         } else {
             const size_t pi = ((size_t)seg * nh + head) * n_splits + split;
             part_o[pi * HD + d] = acc;
@@ -414,7 +440,8 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
             L += __ldcg(part_ml + (p0 + s) * 2 + 1) * f;
             acc += __ldcg(part_o + (p0 + s) * HD + d) * f;
         }
-        out[((size_t)tok * nh + head) * HD + d] = __float2bfloat16_rn(acc / L);
+        out[((size_t)tok * nh + head) * HD + d] =
+            __float2bfloat16_rn(acc / L * gate_of(gate, (size_t)tok * gate_stride + (size_t)head * HD + d));
     }
 }
 
@@ -422,13 +449,14 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
 // grid (64-token tiles, nkv, G / HPW), 128 threads.  A warp owns 16 consecutive tokens of one
 // request and HPW query heads of one kv group; it walks the 16-key blocks up to its last row's
 // position.  tile_seg / tile_q0 list the tiles (a tile never crosses a request).
-template <int HD, int HPW>
+template <int HD, int HPW, bool PSPLIT>
 __global__ void __launch_bounds__(128)
 prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pages,
                          const bf16* __restrict__ v_pages, const int* __restrict__ block_table, int max_pages,
                          int page_size, const int* __restrict__ seg_start, const int* __restrict__ seg_pos0,
                          const int* __restrict__ tile_seg, const int* __restrict__ tile_q0,
-                         bf16* __restrict__ out, int nh, int nkv, int window, float scale_log2) {
+                         bf16* __restrict__ out, int nh, int nkv, int window, float scale_log2, int keep,
+                         const bf16* __restrict__ gate, int gate_stride) {
     // Long tiles first: the queries at the end of a prompt have the most keys to read.  Blocks are handed
     // out in the order of blockIdx.x: the (kv head, head pair) blocks of one tile are neighbours there and
     // the tiles go from the longest to the shortest, a greedy schedule by decreasing work.
@@ -471,18 +499,24 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
 #pragma unroll
         for (int j = 0; j < HD / 8; ++j) o[h][j][0] = o[h][j][1] = o[h][j][2] = o[h][j][3] = 0.f;
     }
+    // with a window that keeps the first keys, their blocks come first, then the walk jumps to the window's
+    const int kb = (window > 0 && keep > 0) ? min((keep + 15) / 16, first_block) : 0;
     KVFrag<HD> cur, nxt;
-    load_block<HD>(cur, k_pages, v_pages, bt, first_block, page_size, nkv, kvh, g, t);
-    for (int b = first_block; b <= last_block; ++b) {
+    int b = kb > 0 ? 0 : first_block;
+    load_block<HD>(cur, k_pages, v_pages, bt, b, page_size, nkv, kvh, g, t);
+    for (;;) {
         const bool more = b < last_block;
-        if (more) load_block<HD>(nxt, k_pages, v_pages, bt, b + 1, page_size, nkv, kvh, g, t);
+        const int b_next = b + 1 == kb ? first_block : b + 1;
+        if (more) load_block<HD>(nxt, k_pages, v_pages, bt, b_next, page_size, nkv, kvh, g, t);
         // a block needs masking if some row cannot see its last key, or a window cuts into it
         const bool need_mask = (b * 16 + 15 > pos_first) || (window > 0 && b * 16 < max(lo_a, lo_b));
 #pragma unroll
         for (int h = 0; h < HPW; ++h)
-            attend_block<HD>(cur, qf[h], qg[h], o[h], m[h], l[h], b * 16, t, pos_a, pos_b, lo_a, lo_b, scale_log2,
-                             need_mask);
-        if (more) cur = nxt;
+            attend_block<HD, true, PSPLIT>(cur, qf[h], qg[h], o[h], m[h], l[h], b * 16, t, pos_a, pos_b, lo_a, lo_b,
+                                           scale_log2, need_mask, keep);
+        if (!more) break;
+        cur = nxt;
+        b = b_next;
     }
 #pragma unroll
     for (int h = 0; h < HPW; ++h) {
@@ -490,12 +524,16 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
         const float ia = 1.f / la, ib = 1.f / lb;
         bf16* oa = out + ((size_t)(t0 + q0 + g) * nh + head0 + h) * HD + 2 * t;
         bf16* ob = out + ((size_t)(t0 + q0 + g + 8) * nh + head0 + h) * HD + 2 * t;
+        const size_t ga = (size_t)(t0 + q0 + g) * gate_stride + (size_t)(head0 + h) * HD + 2 * t;
+        const size_t gb = ga + (size_t)8 * gate_stride;
 #pragma unroll
         for (int j = 0; j < HD / 8; ++j) {
             if (g < rows)
-                *reinterpret_cast<__nv_bfloat162*>(oa + 8 * j) = __floats2bfloat162_rn(o[h][j][0] * ia, o[h][j][1] * ia);
+                *reinterpret_cast<__nv_bfloat162*>(oa + 8 * j) = __floats2bfloat162_rn(
+                    o[h][j][0] * ia * gate_of(gate, ga + 8 * j), o[h][j][1] * ia * gate_of(gate, ga + 8 * j + 1));
             if (g + 8 < rows)
-                *reinterpret_cast<__nv_bfloat162*>(ob + 8 * j) = __floats2bfloat162_rn(o[h][j][2] * ib, o[h][j][3] * ib);
+                *reinterpret_cast<__nv_bfloat162*>(ob + 8 * j) = __floats2bfloat162_rn(
+                    o[h][j][2] * ib * gate_of(gate, gb + 8 * j), o[h][j][3] * ib * gate_of(gate, gb + 8 * j + 1));
         }
     }
 }
@@ -520,7 +558,8 @@ GESSO_API int gesso_decode_attention(const void* q, const void* k_pages, const v
                                      const int* block_table, int max_pages, int page_size, const int* positions,
                                      void* out, int n_segs, int nh, int nkv, int hd,
                                      int window, float scale, int n_splits, float* part_o, float* part_ml,
-                                     int* tickets, const int* kv_span, cudaStream_t stream) {
+                                     int* tickets, const int* kv_span, int keep, const void* gate, int gate_stride,
+                                     int psplit, cudaStream_t stream) {
     if (n_segs <= 0) return 0;
     if (!gesso_attention_tc_takes(hd, page_size, nh, nkv)) return GESSO_ERR_BAD_SIZE;
     const int G = nh / nkv;
@@ -544,19 +583,21 @@ GESSO_API int gesso_decode_attention(const void* q, const void* k_pages, const v
     const size_t ring = (size_t)stages * (hd / 16 * 16 + hd / 8 * 8) * 128;
     const size_t smem = ring > merge ? ring : merge;
     const float scale_log2 = scale * LOG2E;
-#define GO3(HD, ST, UP)                                                                                     \
+#define GO4(HD, ST, UP, PS)                                                                                 \
     do {                                                                                                    \
         static bool configured = false;   /* once per instantiation, outside any stream capture */          \
         if (!configured) {                                                                                  \
-            cudaFuncSetAttribute(decode_attention_kernel<HD, ST, UP>,                                       \
+            cudaFuncSetAttribute(decode_attention_kernel<HD, ST, UP, PS>,                                   \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                   \
             configured = true;                                                                              \
         }                                                                                                   \
-        launch_pdl(decode_attention_kernel<HD, ST, UP>, grid, dim3(128), smem, stream,                      \
+        launch_pdl(decode_attention_kernel<HD, ST, UP, PS>, grid, dim3(128), smem, stream,                  \
             (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_pages, page_size,  \
             page_shift, positions, (bf16*)out, nh, nkv, window, scale_log2, n_splits, part_o, part_ml,      \
-            tickets, kv_span, slots);                                                                       \
+            tickets, kv_span, slots, keep, (const bf16*)gate, gate_stride);                                 \
     } while (0)
+#define GO3(HD, ST, UP)                                                                                     \
+    do { if (psplit) GO4(HD, ST, UP, true); else GO4(HD, ST, UP, false); } while (0)
 #define GO(HD)                                                                                              \
     do {                                                                                                    \
         if (wide) { if (G > 8) GO3(HD, DA_STAGES_WIDE, true); else GO3(HD, DA_STAGES_WIDE, false); }        \
@@ -568,27 +609,33 @@ GESSO_API int gesso_decode_attention(const void* q, const void* k_pages, const v
     else GO(128);
 #undef GO
 #undef GO3
+#undef GO4
     return launch_status();
 }
 
 GESSO_API int gesso_prefill_attention(const void* q, const void* k_pages, const void* v_pages,
                                       const int* block_table, int max_pages, int page_size, const int* seg_start,
                                       const int* seg_pos0, const int* tile_seg, const int* tile_q0, int n_tiles,
-                                      void* out, int nh, int nkv, int hd, int window, float scale, cudaStream_t stream) {
+                                      void* out, int nh, int nkv, int hd, int window, float scale, int keep,
+                                      const void* gate, int gate_stride, int psplit, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (!gesso_attention_tc_takes(hd, page_size, nh, nkv)) return GESSO_ERR_BAD_SIZE;
     const int G = nh / nkv;
     if ((long long)n_tiles * nh > 2147483647LL) return GESSO_ERR_BAD_SIZE;
     const float scale_log2 = scale * LOG2E;
-#define GO(HD, HPW)                                                                                          \
-    prefill_attention_kernel<HD, HPW><<<dim3((unsigned)(n_tiles * nkv * (G / HPW))), 128, 0, stream>>>(      \
+#define GO2(HD, HPW, PS)                                                                                     \
+    prefill_attention_kernel<HD, HPW, PS><<<dim3((unsigned)(n_tiles * nkv * (G / HPW))), 128, 0, stream>>>(  \
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_pages, page_size,       \
-        seg_start, seg_pos0, tile_seg, tile_q0, (bf16*)out, nh, nkv, window, scale_log2)
+        seg_start, seg_pos0, tile_seg, tile_q0, (bf16*)out, nh, nkv, window, scale_log2, keep,               \
+        (const bf16*)gate, gate_stride)
+#define GO(HD, HPW)                                                                                          \
+    do { if (psplit) GO2(HD, HPW, true); else GO2(HD, HPW, false); } while (0)
     if (hd <= 64 && G % 2 == 0) {
         if (hd == 32) GO(32, 2); else GO(64, 2);
     } else {
         if (hd == 32) GO(32, 1); else if (hd == 64) GO(64, 1); else if (hd == 96) GO(96, 1); else GO(128, 1);
     }
 #undef GO
+#undef GO2
     return launch_status();
 }

@@ -57,7 +57,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                  int max_pages, int page_size, const int* __restrict__ seg_start,
                                  const int* __restrict__ seg_pos0, const int* __restrict__ tile_seg,
                                  const int* __restrict__ tile_q0, bf16* __restrict__ out, int nh, int nkv, int G,
-                                 int window, float scale_log2, int num_pages, int* __restrict__ status) {
+                                 int window, float scale_log2, int num_pages, int* __restrict__ status, int keep,
+                                 const bf16* __restrict__ gate, int gate_stride) {
     extern __shared__ unsigned char fa_raw[];
     FaSmem& s = *reinterpret_cast<FaSmem*>(((size_t)fa_raw + 1023) & ~(size_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -84,7 +85,11 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const int pos_first = p0 + q0, pos_last = p0 + q0 + rows_tok - 1;
     const int first_key = window > 0 ? max(0, pos_first - window + 1) : 0;
     const int kb0 = first_key / FA_BK, kb1 = pos_last / FA_BK;         // key blocks kb0..kb1
-    const int n_blocks = kb1 - kb0 + 1;
+    // With a window that keeps the first `keep` keys visible, the blocks of those keys come ahead of the
+    // window's: every role walks a list of ks + (kb1 - kb0 + 1) blocks, `kblk` turns a place in it into a block.
+    const int ks = (window > 0 && keep > 0) ? min((keep + FA_BK - 1) / FA_BK, kb0) : 0;
+    const int n_blocks = ks + kb1 - kb0 + 1;
+    auto kblk = [&](int j) { return j < ks ? j : kb0 + (j - ks); };
     const int* bt = block_table + (size_t)seg * max_pages;
 
     if (threadIdx.x == 0) {
@@ -136,7 +141,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         // are exact zeros, but 0 x NaN is NaN and such a page may hold anything, so nothing of it is
         // read: its loads start past the last row of the tensor map, where TMA fills in zeros.
         auto lookup = [&](int j) -> int {
-            const int key0 = (kb0 + j) * FA_BK + lane * 16;
+            const int key0 = kblk(j) * FA_BK + lane * 16;
             return (lane < FA_BK / 16 && j < n_blocks && key0 <= pos_last) ? bt[key0 / page_size] : -1;
         };
         unsigned long long* full = keys ? s.k_full : s.v_full;
@@ -152,7 +157,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             }
             ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
             if (ok && lane < FA_BK / 16) {
-                const int sl = ((kb0 + j) * FA_BK + lane * 16) % page_size;
+                const int sl = (kblk(j) * FA_BK + lane * 16) % page_size;
                 const int pg = page < 0 ? num_pages : page;          // num_pages: the first row past the end
                 if (keys) tma_load_2d(s.k[st] + lane * 16 * FA_HD, &map_k, 0, (pg * nkv + kvh) * page_size + sl, &full[st]);
                 else tma_load_2d(s.v[st] + lane * 16 * FA_HD, &map_v, sl, (pg * nkv + kvh) * FA_HD, &full[st]);
@@ -227,7 +232,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             return false;
         };
         for (int j = 0; j < n_blocks && ok; ++j) {
-            const int key0 = (kb0 + j) * FA_BK;
+            const int key0 = kblk(j) * FA_BK;
             if (!wait_all(&s.s_full, j & 1, 16)) { ok = false; break; }
             tc_fence_after();
             unsigned v[FA_BK];
@@ -242,7 +247,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
                 for (int i = 0; i < FA_BK; ++i) {
                     const int key = key0 + i;
-                    if (key > pos || key < lo) v[i] = 0xff800000u;      // -inf
+                    if (key > pos || (key < lo && key >= keep)) v[i] = 0xff800000u;      // -inf
                 }
             }
             // four independent chains of three-input maxima: 64 instructions for 128 scores
@@ -316,6 +321,9 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             tc_fence_after();
             const float inv = 1.f / l;
             bf16* dst = out + ((size_t)(t0 + q0 + tok) * nh + (size_t)kvh * G + hg) * FA_HD;
+            // an output gate: the result times sigmoid(gate), read from rows gate_stride elements apart
+            const bf16* grow = (gate && valid) ? gate + (size_t)(t0 + q0 + tok) * gate_stride + ((size_t)kvh * G + hg) * FA_HD
+                                               : nullptr;
 #pragma unroll
             for (int c = 0; c < FA_HD; c += 32) {
                 unsigned o[32];
@@ -327,8 +335,12 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                         unsigned w4[4];
 #pragma unroll
                         for (int i = 0; i < 8; i += 2) {
-                            __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(o[d + i]) * inv,
-                                                                      __uint_as_float(o[d + i + 1]) * inv);
+                            float y0 = __uint_as_float(o[d + i]) * inv, y1 = __uint_as_float(o[d + i + 1]) * inv;
+                            if (grow) {
+                                y0 *= 1.f / (1.f + __expf(-__bfloat162float(grow[c + d + i])));
+                                y1 *= 1.f / (1.f + __expf(-__bfloat162float(grow[c + d + i + 1])));
+                            }
+                            __nv_bfloat162 b2 = __floats2bfloat162_rn(y0, y1);
                             w4[i / 2] = *reinterpret_cast<unsigned*>(&b2);
                         }
                         *reinterpret_cast<uint4*>(dst + c + d) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
@@ -358,8 +370,10 @@ GESSO_API int gesso_prefill_attention_tcgen05(const void* q, const void* k_pages
                                               const int* block_table, int max_pages, int page_size,
                                               const int* seg_start, const int* seg_pos0, const int* tile_seg,
                                               const int* tile_q0, int n_tiles, int n_tokens, void* out, int nh, int nkv,
-                                              int window, float scale, int* status, cudaStream_t stream) {
+                                              int window, float scale, int* status, int keep, const void* gate,
+                                              int gate_stride, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
+    if (keep < 0 || (gate && gate_stride < nh * FA_HD)) return GESSO_ERR_BAD_SIZE;
     if (!gesso_attention_tcgen05_takes(FA_HD, page_size, nh, nkv)) return GESSO_ERR_BAD_SIZE;
     TensorMapEncodeFn fn = tensor_map_encoder();
     if (!fn) return GESSO_ERR_UNSUPPORTED;
@@ -408,6 +422,6 @@ GESSO_API int gesso_prefill_attention_tcgen05(const void* q, const void* k_pages
     const dim3 grid((unsigned)(n_tiles * sub * nkv));
     launch_pdl(prefill_attention_tcgen05_kernel, grid, dim3(FA_THREADS), smem, stream,
         mq, mk, mv, block_table, max_pages, page_size, seg_start, seg_pos0, tile_seg, tile_q0, (bf16*)out, nh, nkv, G,
-        window, scale * FA_LOG2E, num_pages, status);
+        window, scale * FA_LOG2E, num_pages, status, keep, (const bf16*)gate, gate_stride);
     return launch_status();
 }

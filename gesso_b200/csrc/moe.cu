@@ -1,15 +1,16 @@
 // Routed feed-forward (mixture of experts): the router, and the expert products for steps of few rows.
 //
-// Router (one warp per token, all float32):
-//   z_e = w_router[e] . x,  s_e = score(z_e)  (sigmoid, or softmax over the experts),
+// Router (one warp per token, all float32).  The logits z = W_router x come from a matrix product with float32
+// accumulation (bfloat16 operands are exact in it, so a bfloat16 run's logits are the float32 sums of the same
+// numbers); this kernel does the rest:
+//   s_e = score(z_e)  (sigmoid, or softmax over the experts),
 //   c_e = s_e + correction[e]                  (the score an expert is CHOSEN by; the weight uses s_e),
 //   experts form `n_groups` equal groups of neighbours; a group's score is the sum of its `group_top`
 //   largest c_e; only experts of the `keep_groups` best groups can be chosen (the others' c_e count as
 //   -inf); the `top` largest c_e among those are chosen (ties: the lower index);
 //   weight_k = s_e of the chosen expert, divided by the sum of the chosen weights with `renorm`,
 //   times `weight_scale`.
-// Every sum runs in a fixed order (lanes stride over the features, then a butterfly), so a token's choice
-// and weights do not depend on what else is in the step.
+// A token's choice and weights depend on its own logits only, not on what else is in the step.
 //
 // Expert products by (token, chosen expert) pair, for steps of few tokens, for the float32 path and for
 // sizes the tensor-core path does not take: `moe_pair_up` computes act[pair] = act_fn(W_up[e] x) (a block
@@ -29,10 +30,9 @@ __device__ __forceinline__ float moe_act(float v, int act) {
     return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
 }
 
-template <typename T>
 __global__ void __launch_bounds__(128)
-moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w_router, const float* __restrict__ correction,
-                 int* __restrict__ top_idx, float* __restrict__ top_w, int n_tokens, int H, int E, int top,
+moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ correction,
+                 int* __restrict__ top_idx, float* __restrict__ top_w, int n_tokens, int E, int top,
                  int n_groups, int keep_groups, int group_top, int score_fn, int renorm, float weight_scale) {
     extern __shared__ float moe_smem[];
     pdl_launch_dependents();
@@ -43,14 +43,7 @@ moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w_router, co
     float* s = moe_smem + (size_t)wid * (2 * E + n_groups);   // scores
     float* c = s + E;                                           // choice scores (-inf once taken or shut out)
     float* gs = c + E;                                          // group scores
-    const T* xr = x + (size_t)t * H;
-    for (int e = 0; e < E; ++e) {
-        const float* wr = w_router + (size_t)e * H;
-        float acc = 0.f;
-        for (int j = lane; j < H; j += 32) acc += wr[j] * to_f32(xr[j]);
-        acc = warp_sum(acc);
-        if (lane == 0) s[e] = acc;
-    }
+    for (int e = lane; e < E; e += 32) s[e] = logits[(size_t)t * E + e];
     __syncwarp();
     if (score_fn == MOE_SCORE_SOFTMAX) {
         float m = -INFINITY;
@@ -127,65 +120,75 @@ moe_route_kernel(const T* __restrict__ x, const float* __restrict__ w_router, co
     }
 }
 
-// x [tokens, H] of x_dtype; w_router [E, H] and correction [E] (or null) float32; top_idx / top_w [tokens, top].
-GESSO_API int gesso_moe_route(const void* x, int x_dtype, const float* w_router, const float* correction, int* top_idx,
-                              float* top_w, int n_tokens, int H, int E, int top, int n_groups, int keep_groups,
+// logits [tokens, E] and correction [E] (or null) float32; top_idx / top_w [tokens, top].
+GESSO_API int gesso_moe_route(const float* logits, const float* correction, int* top_idx,
+                              float* top_w, int n_tokens, int E, int top, int n_groups, int keep_groups,
                               int group_top, int score_fn, int renorm, float weight_scale, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (H <= 0 || E <= 0 || top < 1 || top > E || top > 32 || n_groups < 1 || E % n_groups != 0 || keep_groups < 1 ||
+    if (E <= 0 || top < 1 || top > E || top > 32 || n_groups < 1 || E % n_groups != 0 || keep_groups < 1 ||
         keep_groups > n_groups || group_top < 1 || group_top > 2 || (E / n_groups) * keep_groups < top)
         return GESSO_ERR_BAD_SIZE;
     const size_t smem = (size_t)4 * (2 * E + n_groups) * sizeof(float);
     if (smem > 48 * 1024) return GESSO_ERR_BAD_SIZE;
     const dim3 grid((n_tokens + 3) / 4);
-    if (x_dtype == GESSO_F32)
-        launch_pdl(moe_route_kernel<float>, grid, dim3(128), smem, stream, (const float*)x, w_router, correction, top_idx,
-                   top_w, n_tokens, H, E, top, n_groups, keep_groups, group_top, score_fn, renorm, weight_scale);
-    else if (x_dtype == GESSO_BF16)
-        launch_pdl(moe_route_kernel<bf16>, grid, dim3(128), smem, stream, (const bf16*)x, w_router, correction, top_idx,
-                   top_w, n_tokens, H, E, top, n_groups, keep_groups, group_top, score_fn, renorm, weight_scale);
-    else
-        return GESSO_ERR_BAD_DTYPE;
+    launch_pdl(moe_route_kernel, grid, dim3(128), smem, stream, logits, correction, top_idx, top_w, n_tokens, E, top,
+               n_groups, keep_groups, group_top, score_fn, renorm, weight_scale);
     return launch_status();
 }
 
 // ---- expert products by (token, expert) pair -------------------------------------------------------------
-// dot of a weight row with a float32 vector in shared memory: lanes stride over 8-element pieces (16-byte
-// reads of bfloat16, two of float32) when the length allows it
-template <typename TW>
-__device__ __forceinline__ float row_dot(const TW* __restrict__ w, const float* __restrict__ v, int K, int lane);
-
-template <>
-__device__ __forceinline__ float row_dot<bf16>(const bf16* __restrict__ w, const float* __restrict__ v, int K, int lane) {
-    float acc = 0.f;
-    if (K % 8 == 0 && ((size_t)w & 15) == 0) {
-        for (int j = lane * 8; j < K; j += 256) {
-            const uint4 u = *reinterpret_cast<const uint4*>(w + j);
-            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+// Dots of R weight rows (`stride` elements apart) with one float32 vector in shared memory.  All R rows' loads of
+// a step are issued before any is used, so a lane keeps R 16-byte reads in flight: these kernels are bound by
+// the latency of the weight stream, not by arithmetic.  Lanes stride over 8-element pieces (16-byte reads of
+// bfloat16, two of float32) when the length and the alignment allow it.
+template <typename TW> struct Piece;
+template <> struct Piece<bf16> {
+    uint4 u;
+    __device__ __forceinline__ void load(const bf16* p) { u = *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ float dot(const float* v) const {
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+        float acc = 0.f;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) acc += __low2float(p[i]) * v[j + 2 * i] + __high2float(p[i]) * v[j + 2 * i + 1];
+        for (int i = 0; i < 4; ++i) acc += __low2float(p[i]) * v[2 * i] + __high2float(p[i]) * v[2 * i + 1];
+        return acc;
+    }
+};
+template <> struct Piece<float> {
+    float4 a, b;
+    __device__ __forceinline__ void load(const float* p) {
+        a = *reinterpret_cast<const float4*>(p);
+        b = *reinterpret_cast<const float4*>(p + 4);
+    }
+    __device__ __forceinline__ float dot(const float* v) const {
+        return a.x * v[0] + a.y * v[1] + a.z * v[2] + a.w * v[3] + b.x * v[4] + b.y * v[5] + b.z * v[6] + b.w * v[7];
+    }
+};
+
+template <typename TW, int R>
+__device__ __forceinline__ void rows_dot(const TW* __restrict__ w, size_t stride, int n_rows, const float* __restrict__ v,
+                                         int K, int lane, float (&out)[R]) {
+    float acc[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[r] = 0.f;
+    if (K % 8 == 0 && ((size_t)w & 15) == 0 && (stride * sizeof(TW)) % 16 == 0) {
+        for (int j = lane * 8; j < K; j += 256) {
+            Piece<TW> pc[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) pc[r].load(w + (size_t)(r < n_rows ? r : 0) * stride + j);
+#pragma unroll
+            for (int r = 0; r < R; ++r) acc[r] += pc[r].dot(v + j);
         }
     } else {
-        for (int j = lane; j < K; j += 32) acc += __bfloat162float(w[j]) * v[j];
-    }
-    return warp_sum(acc);
-}
-
-template <>
-__device__ __forceinline__ float row_dot<float>(const float* __restrict__ w, const float* __restrict__ v, int K, int lane) {
-    float acc = 0.f;
-    if (K % 4 == 0 && ((size_t)w & 15) == 0) {
-        for (int j = lane * 4; j < K; j += 128) {
-            const float4 u = *reinterpret_cast<const float4*>(w + j);
-            acc += u.x * v[j] + u.y * v[j + 1] + u.z * v[j + 2] + u.w * v[j + 3];
+        for (int j = lane; j < K; j += 32) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) acc[r] += to_f32(w[(size_t)(r < n_rows ? r : 0) * stride + j]) * v[j];
         }
-    } else {
-        for (int j = lane; j < K; j += 32) acc += w[j] * v[j];
     }
-    return warp_sum(acc);
+#pragma unroll
+    for (int r = 0; r < R; ++r) out[r] = warp_sum(acc[r]);
 }
 
-#define MOE_PAIR_OUTS 32      // outputs per block (8 per warp)
+#define MOE_PAIR_OUTS 32      // outputs per block (8 per warp, taken together)
 
 template <typename TX, typename TW>
 __global__ void __launch_bounds__(128)
@@ -200,10 +203,16 @@ moe_pair_up_kernel(const TX* __restrict__ x, const TW* __restrict__ w_up, const 
     const int e = top_idx[pair];
     for (int j = threadIdx.x; j < K; j += 128) moe_smem[j] = to_f32(x[(size_t)tok * K + j]);
     __syncthreads();
-    const TW* w = w_up + (size_t)e * F * K;
-    for (int f = f0 + wid; f < min(F, f0 + MOE_PAIR_OUTS); f += 4) {
-        const float v = row_dot<TW>(w + (size_t)f * K, moe_smem, K, lane);
-        if (lane == 0) act_out[(size_t)pair * F + f] = from_f32<TX>(moe_act(v, act));
+    const int f = f0 + 8 * wid;                       // this warp's eight outputs
+    if (f >= F) return;
+    const int n_rows = min(8, F - f);
+    float v[8];
+    rows_dot<TW, 8>(w_up + ((size_t)e * F + f) * K, (size_t)K, n_rows, moe_smem, K, lane, v);
+    if (lane < n_rows) {
+        float mine = v[0];
+#pragma unroll
+        for (int r = 1; r < 8; ++r) mine = lane == r ? v[r] : mine;
+        act_out[(size_t)pair * F + f + lane] = from_f32<TX>(moe_act(mine, act));
     }
 }
 
@@ -218,14 +227,23 @@ moe_pair_down_kernel(const TX* __restrict__ act_in, const TW* __restrict__ w_dow
     pdl_wait();
     for (int j = threadIdx.x; j < top * F; j += 128) moe_smem[j] = to_f32(act_in[(size_t)tok * top * F + j]);
     __syncthreads();
-    for (int n = n0 + wid; n < min(N, n0 + MOE_PAIR_OUTS); n += 4) {
-        float sum = 0.f;
-        for (int k = 0; k < top; ++k) {
-            const int e = top_idx[(size_t)tok * top + k];
-            const float v = row_dot<TW>(w_down + ((size_t)e * N + n) * F, moe_smem + (size_t)k * F, F, lane);
-            sum += top_w[(size_t)tok * top + k] * v;
-        }
-        if (lane == 0) y[(size_t)tok * N + n] = sum;
+    const int n = n0 + 8 * wid;                       // this warp's eight outputs
+    if (n >= N) return;
+    const int n_rows = min(8, N - n);
+    float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < top; ++k) {                   // in the order of the choice
+        const int e = top_idx[(size_t)tok * top + k];
+        const float wk = top_w[(size_t)tok * top + k];
+        float v[8];
+        rows_dot<TW, 8>(w_down + ((size_t)e * N + n) * F, (size_t)F, n_rows, moe_smem + (size_t)k * F, F, lane, v);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) sum[r] += wk * v[r];
+    }
+    if (lane < n_rows) {
+        float mine = sum[0];
+#pragma unroll
+        for (int r = 1; r < 8; ++r) mine = lane == r ? sum[r] : mine;
+        y[(size_t)tok * N + n + lane] = mine;
     }
 }
 

@@ -22,11 +22,13 @@
 // The position part may rotate only the first `rot_dim` features of a head (the rest are normed and
 // passed on as they are) and may pair neighbours (2i, 2i+1) instead of the halves (i, i + rot_dim/2);
 // the tables are [max_positions, rot_dim/2] then.  The kernel that works by 64-token tiles takes the
-// full half-split layout only; everything else goes through the one below.
+// half-split layout with a rotated part that is a multiple of 8 features; everything else goes through the
+// one below.
 //
 // The projection may carry biases (a float32 vector along the fused row, added before norm and rotation, and
 // to v), values of another width than the keys (`vd`), and further columns behind the v heads that this
-// kernel leaves alone (`row_stride` elements per token); the per-token kernel takes all of these.
+// kernel leaves alone (`row_stride` elements per token); the per-token kernel takes all of these, the tile
+// kernel all but another value width.
 //
 // One warp per (token, head).  Everything is float32 inside; stores round to the run type.
 #include "common.cuh"
@@ -125,7 +127,8 @@ qk_norm_rope_store_tile_kernel(
     const float* __restrict__ cos_t, const float* __restrict__ sin_t, const int* __restrict__ seg_start,
     const int* __restrict__ seg_pos0, const int* __restrict__ tile_seg, const int* __restrict__ tile_q0,
     const int* __restrict__ block_table, int max_pages, int page_size, bf16* __restrict__ q_out,
-    bf16* __restrict__ k_pages, bf16* __restrict__ v_pages, int nh, int nkv, int* __restrict__ status) {
+    bf16* __restrict__ k_pages, bf16* __restrict__ v_pages, int nh, int nkv, int* __restrict__ status,
+    const float* __restrict__ bias, int row_stride, int rot_dim) {
     constexpr int LPH = HD / 8, HALF = HD / 2;
     __shared__ __align__(16) bf16 vt[64][HD + 8];
     // launched programmatically: let the successor be set up, then wait for what earlier kernels wrote (every
@@ -138,26 +141,37 @@ qk_norm_rope_store_tile_kernel(
     const int rows = min(64, n - q0);
     if (rows <= 0) return;
     const int pos0 = seg_pos0[seg] + q0;
-    const int heads = nh + 2 * nkv;
     const bool is_q = hs < nh;
     const int kvh = hs - nh;
     const int* bt = block_table + (size_t)seg * max_pages;
     const float* w = is_q ? q_w : k_w;
     const bool rotate = cos_t != nullptr;
     const int l = threadIdx.x % LPH;
+    // A lane holds two pieces of four features, `ca` and `cb`.  Where the whole head rotates they are the
+    // partners of the two halves (4l and HD/2 + 4l).  Where only the first rot_dim features rotate, the first
+    // rot_dim / 8 lanes hold partners (4l and rot_dim/2 + 4l) and the others eight features that pass through.
+    const int rl = rotate ? rot_dim / 8 : 0;
+    const bool rot_lane = l < rl;
+    const int ca = !rotate ? 4 * l : rot_lane ? 4 * l : rot_dim + 8 * (l - rl);
+    const int cb = !rotate ? HALF + 4 * l : rot_lane ? rot_dim / 2 + 4 * l : ca + 4;
+    const float* bs = bias ? bias + (size_t)hs * HD : nullptr;       // q heads, then k heads, along the fused row
     for (int r0 = threadIdx.x / LPH; r0 < 64; r0 += 256 / LPH) {      // the same trip count for every lane
         const bool valid = r0 < rows;
         const int r = valid ? r0 : rows - 1;
         const int t = t0 + q0 + r, pos = pos0 + r;
-        const bf16* src = qkv + ((size_t)t * heads + hs) * HD;
-        const uint2 ua = *reinterpret_cast<const uint2*>(src + 4 * l);
-        const uint2 ub = *reinterpret_cast<const uint2*>(src + HALF + 4 * l);
+        const bf16* src = qkv + (size_t)t * row_stride + (size_t)hs * HD;
+        const uint2 ua = *reinterpret_cast<const uint2*>(src + ca);
+        const uint2 ub = *reinterpret_cast<const uint2*>(src + cb);
         float a[4], b[4];
         {
             const __nv_bfloat162 a0 = *reinterpret_cast<const __nv_bfloat162*>(&ua.x), a1 = *reinterpret_cast<const __nv_bfloat162*>(&ua.y);
             const __nv_bfloat162 b0 = *reinterpret_cast<const __nv_bfloat162*>(&ub.x), b1 = *reinterpret_cast<const __nv_bfloat162*>(&ub.y);
             a[0] = __low2float(a0); a[1] = __high2float(a0); a[2] = __low2float(a1); a[3] = __high2float(a1);
             b[0] = __low2float(b0); b[1] = __high2float(b0); b[2] = __low2float(b1); b[3] = __high2float(b1);
+        }
+        if (bs) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { a[i] += bs[ca + i]; b[i] += bs[cb + i]; }
         }
         float ss = 0.f;
 #pragma unroll
@@ -166,15 +180,15 @@ qk_norm_rope_store_tile_kernel(
         for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
         if (w) {
             const float denom = sqrtf(ss / (float)HD + eps);
-            const float4 wa = *reinterpret_cast<const float4*>(w + 4 * l);
-            const float4 wb = *reinterpret_cast<const float4*>(w + HALF + 4 * l);
+            const float4 wa = *reinterpret_cast<const float4*>(w + ca);
+            const float4 wb = *reinterpret_cast<const float4*>(w + cb);
             a[0] = (a[0] / denom) * wa.x; a[1] = (a[1] / denom) * wa.y; a[2] = (a[2] / denom) * wa.z; a[3] = (a[3] / denom) * wa.w;
             b[0] = (b[0] / denom) * wb.x; b[1] = (b[1] / denom) * wb.y; b[2] = (b[2] / denom) * wb.z; b[3] = (b[3] / denom) * wb.w;
         }
         float c[4] = {1.f, 1.f, 1.f, 1.f}, sn[4] = {0.f, 0.f, 0.f, 0.f};
-        if (rotate) {
-            const float4 cc = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * HALF + 4 * l);
-            const float4 sv = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * HALF + 4 * l);
+        if (rot_lane) {
+            const float4 cc = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * (rot_dim / 2) + 4 * l);
+            const float4 sv = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * (rot_dim / 2) + 4 * l);
             c[0] = cc.x; c[1] = cc.y; c[2] = cc.z; c[3] = cc.w;
             sn[0] = sv.x; sn[1] = sv.y; sn[2] = sv.z; sn[3] = sv.w;
         }
@@ -199,16 +213,24 @@ qk_norm_rope_store_tile_kernel(
             oa.x = *reinterpret_cast<unsigned*>(&v0); oa.y = *reinterpret_cast<unsigned*>(&v1);
             ob.x = *reinterpret_cast<unsigned*>(&v2); ob.y = *reinterpret_cast<unsigned*>(&v3);
         }
-        *reinterpret_cast<uint2*>(dst + 4 * l) = oa;
-        *reinterpret_cast<uint2*>(dst + HALF + 4 * l) = ob;
+        *reinterpret_cast<uint2*>(dst + ca) = oa;
+        *reinterpret_cast<uint2*>(dst + cb) = ob;
     }
     if (is_q) return;
     // ---- the v head of this kv head: tile -> shared memory -> transposed pages ----
     for (int idx = threadIdx.x; idx < 64 * (HD / 8); idx += 256) {
         const int r = idx / (HD / 8), cpiece = idx % (HD / 8);
-        if (r < rows)
-            *reinterpret_cast<uint4*>(&vt[r][8 * cpiece]) = *reinterpret_cast<const uint4*>(
-                qkv + ((size_t)(t0 + q0 + r) * heads + nh + nkv + kvh) * HD + 8 * cpiece);
+        if (r < rows) {
+            const int col = (nh + nkv + kvh) * HD + 8 * cpiece;
+            uint4 u = *reinterpret_cast<const uint4*>(qkv + (size_t)(t0 + q0 + r) * row_stride + col);
+            if (bias) {
+                __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    p2[i] = __floats2bfloat162_rn(__low2float(p2[i]) + bias[col + 2 * i], __high2float(p2[i]) + bias[col + 2 * i + 1]);
+            }
+            *reinterpret_cast<uint4*>(&vt[r][8 * cpiece]) = u;
+        }
     }
     __syncthreads();
     const int g0 = pos0 >> 3, ng = ((pos0 + rows - 1) >> 3) - g0 + 1;      // groups of 8 positions
@@ -258,14 +280,19 @@ GESSO_API int gesso_qk_norm_rope_store_tiles(const void* qkv, const float* q_w, 
                                              const int* seg_pos0, const int* tile_seg, const int* tile_q0,
                                              int n_tiles, const int* block_table, int max_pages, int page_size,
                                              void* q_out, void* k_pages, void* v_pages, int nh, int nkv, int hd,
-                                             int* status, cudaStream_t stream) {
+                                             int* status, const float* bias, int row_stride, int rot_dim,
+                                             cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (!gesso_qk_rope_store_tiles_takes(hd, page_size, nh, nkv)) return GESSO_ERR_BAD_SIZE;
+    if (row_stride <= 0) row_stride = (nh + 2 * nkv) * hd;
+    if (rot_dim <= 0) rot_dim = hd;
+    // 16-byte pieces: the rotated part in whole lanes, rows 16-byte aligned
+    if (row_stride < (nh + 2 * nkv) * hd || row_stride % 8 != 0 || rot_dim % 8 != 0 || rot_dim > hd) return GESSO_ERR_BAD_SIZE;
     const dim3 grid(n_tiles, nh + nkv);
 #define GO(HD)                                                                                                  \
     launch_pdl(qk_norm_rope_store_tile_kernel<HD>, grid, dim3(256), 0, stream,                                  \
         (const bf16*)qkv, q_w, k_w, eps, cos_t, sin_t, seg_start, seg_pos0, tile_seg, tile_q0, block_table,     \
-        max_pages, page_size, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, nh, nkv, status)
+        max_pages, page_size, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages, nh, nkv, status, bias, row_stride, rot_dim)
     if (hd == 32) GO(32);
     else if (hd == 64) GO(64);
     else GO(128);

@@ -4,7 +4,11 @@ float32 runs always take the FP32-arithmetic kernel.  bfloat16 runs take the ten
 when the sizes fit them (head 32/64/96/128, pages in multiples of 16 slots): the split-KV kernel
 for steps of single tokens; for steps with portions the tcgen05 flash kernel (head 64, 2 to 16 query
 heads per kv head) or else the mma.sync flash kernel; other sizes take the FP32-arithmetic kernel
-on bfloat16 data.  Every branch is one of this library's own kernels.
+on bfloat16 data.  Kept first keys under a window and an output gate are taken by every kernel;
+attention weights in two bfloat16 pieces by the mma.sync kernels and the FP32-arithmetic kernel
+(whose weights are float32 anyway), not by the tcgen05 kernel; values of another width than the keys
+by the FP32-arithmetic kernel only.  Every
+branch is one of this library's own kernels.
 """
 from __future__ import annotations
 
@@ -13,14 +17,14 @@ import torch
 from .. import ops
 
 
-def paged_attention(rt, q, cache, ctx, window, scale, keep_first: int = 0, gate=None):
+def paged_attention(rt, q, cache, ctx, window, scale, keep_first: int = 0, gate=None, split_weights: bool = False):
     N, nh, hd = q.shape
     nkv, page_size = cache.k_pages.shape[1], cache.k_pages.shape[2]
     vd = cache.v_pages.shape[2]
     if window is None:
         keep_first = 0                       # without a window every earlier key is visible anyway
-    plain = vd == hd and not keep_first and gate is None
-    if q.dtype == torch.bfloat16 and plain and ops.fast_attention_takes(hd, page_size, nh, nkv):
+    split_weights = split_weights and ops.ATTN_SPLIT_WEIGHTS
+    if q.dtype == torch.bfloat16 and vd == hd and ops.fast_attention_takes(hd, page_size, nh, nkv):
         if ctx.decode_only:
             splits = ops.decode_splits(ctx.n_segs, nkv, ctx.max_kv_len, uneven=True)
             ws = None
@@ -34,12 +38,13 @@ def paged_attention(rt, q, cache, ctx, window, scale, keep_first: int = 0, gate=
                           torch.zeros((ctx.n_segs * nkv,), dtype=torch.int32, device=dev))
                     rt.shared[key] = ws
             return ops.decode_attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions,
-                                        window, scale, splits, ws, ctx.kv_span)
-        if ops.attention_tcgen05_takes(hd, page_size, nh, nkv):
+                                        window, scale, splits, ws, ctx.kv_span, keep_first, gate, split_weights)
+        if not split_weights and ops.attention_tcgen05_takes(hd, page_size, nh, nkv):
             # head 64 with 2..16 query heads per kv head: S and P in tensor memory, pages by TMA
             return ops.prefill_attention_tcgen05(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.seg_start,
-                                                 ctx.seg_pos0, ctx.tile_seg, ctx.tile_q0, window, scale)
+                                                 ctx.seg_pos0, ctx.tile_seg, ctx.tile_q0, window, scale, keep_first, gate)
         return ops.prefill_attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.seg_start,
-                                     ctx.seg_pos0, ctx.tile_seg, ctx.tile_q0, window, scale)
+                                     ctx.seg_pos0, ctx.tile_seg, ctx.tile_q0, window, scale, keep_first, gate,
+                                     split_weights)
     return ops.paged_attention_generic(q, cache.k_pages, cache.v_pages, cache.block_table,
                                        ctx.positions, ctx.seg_of_token, window, scale, keep_first, gate)

@@ -37,10 +37,10 @@ class Runtime:
         self.max_positions = int(max_positions)
         self.shared: Dict = {}
 
-    def attention(self, q, cache, ctx, window, scale, keep_first: int = 0, gate=None):
+    def attention(self, q, cache, ctx, window, scale, keep_first: int = 0, gate=None, split_weights: bool = False):
         """Attention of the step's queries over the paged cache (kernel choice lives here)."""
         from . import attention_dispatch
-        return attention_dispatch.paged_attention(self, q, cache, ctx, window, scale, keep_first, gate)
+        return attention_dispatch.paged_attention(self, q, cache, ctx, window, scale, keep_first, gate, split_weights)
 
 
 @dataclass

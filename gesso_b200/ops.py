@@ -181,20 +181,21 @@ MOE_ACTS = {"relu2": 0, "silu": 1, "gelu_tanh": 2}
 def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], top: int, n_groups: int,
               keep_groups: int, group_top: int = 2, score: str = "sigmoid", renorm: bool = False,
               weight_scale: float = 1.0):
-    """Router of a mixture of experts, float32: returns ``(expert ids int32 [N, top], weights float32 [N, top])``
-    in the order of the choice (best first)."""
-    _cuda_contig(x, "x")
-    _cuda_contig(w_router, "router weight", torch.float32)
-    N, H = x.shape
+    """Router of a mixture of experts: returns ``(expert ids int32 [N, top], weights float32 [N, top])`` in the
+    order of the choice (best first).  The logits are a matrix product with float32 accumulation and a float32
+    result (:func:`linear`: products of bfloat16 numbers are exact there, a float32 operand takes the FP32 FMA
+    kernel); scores, correction, groups, choice and weights are one float32 kernel."""
+    N = x.shape[0]
     E = w_router.shape[0]
-    _need(w_router.shape[1] == H, "router width differs from the row width")
+    logits = linear(x, w_router, out_dtype=torch.float32)
+    _cuda_contig(logits, "router logits", torch.float32)
     if correction is not None:
         _cuda_contig(correction, "correction", torch.float32)
         _need(correction.numel() == E, "one correction per expert")
     idx = torch.empty((N, top), dtype=torch.int32, device=x.device)
     w = torch.empty((N, top), dtype=torch.float32, device=x.device)
     _lib.check(_lib.library().gesso_moe_route(
-        _p(x), _dt(x), _p(w_router), _p(correction), _p(idx), _p(w), N, H, E, int(top), int(n_groups), int(keep_groups),
+        _p(logits), _p(correction), _p(idx), _p(w), N, E, int(top), int(n_groups), int(keep_groups),
         int(group_top), MOE_SCORES[score], 1 if renorm else 0, float(weight_scale), _stream()), "moe_route")
     return idx, w
 
@@ -221,9 +222,65 @@ def moe_experts_pairs(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
     return y
 
 
+# Steps with at most this many (token, expert) pairs go pair by pair (each pair streams its expert's
+# matrices: the rate of a decoding step); more pairs are grouped by expert for the tensor cores.
+MOE_PAIR_MAX_ROWS = int(os.environ.get("GESSO_MOE_PAIR_MAX_ROWS", "128"))
+
+
+_lib.declare("gesso_moe_grouped_rows", [_lib.LL, _lib.I])
+_lib.declare("gesso_moe_grouped_takes", [_lib.I, _lib.I, _lib.I])
+_lib.declare("gesso_moe_group_rows", [_lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P, _lib.P])
+_lib.declare("gesso_moe_gather_rows", [_lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.I, _lib.P])
+_lib.declare("gesso_moe_combine", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.I, _lib.P])
+_lib.declare("gesso_moe_gemm_tcgen05", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.P, _lib.LL, _lib.I, _lib.I, _lib.I, _lib.I,
+                                        _lib.I, _lib.P, _lib.P])
+
+
 def moe_grouped_takes(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, top: int) -> bool:
-    """Whether the grouped tensor-core path takes this step (see :func:`moe_experts_grouped`)."""
-    return False
+    """Whether the grouped tensor-core path takes this step (see :func:`moe_experts_grouped`): bfloat16 rows and
+    matrices, more pairs than go pair by pair, sizes in multiples of 8."""
+    E, F, K = w_up.shape
+    return (x.dtype == torch.bfloat16 and w_up.dtype == torch.bfloat16 and w_down.dtype == torch.bfloat16
+            and x.shape[0] * top > MOE_PAIR_MAX_ROWS
+            and bool(_lib.library().gesso_moe_grouped_takes(K, F, w_down.shape[1])))
+
+
+def moe_experts_grouped(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, idx: torch.Tensor, w: torch.Tensor,
+                        act: str = "relu2") -> torch.Tensor:
+    """The same sum as :func:`moe_experts_pairs` with the rows grouped by expert and both products on the
+    tcgen05 tensor cores (``csrc/moe_grouped.cu``); float32 [N, H].  Nothing here waits for the device: how
+    many row tiles the routing made stays in device memory."""
+    _cuda_contig(x, "x", torch.bfloat16)
+    _cuda_contig(w_up, "w_up", torch.bfloat16)
+    _cuda_contig(w_down, "w_down", torch.bfloat16)
+    _cuda_contig(idx, "expert ids", torch.int32)
+    _cuda_contig(w, "expert weights", torch.float32)
+    N, K = x.shape
+    E, F, K2 = w_up.shape
+    Hout = w_down.shape[1]
+    _need(K2 == K and tuple(w_down.shape) == (E, Hout, F), "expert matrices do not fit the rows")
+    top = idx.shape[1]
+    pairs = N * top
+    lib = _lib.library()
+    rows = int(lib.gesso_moe_grouped_rows(pairs, E))
+    dev = x.device
+    pair_row = torch.empty((pairs,), dtype=torch.int32, device=dev)
+    tile_expert = torch.empty((rows // 128 + 1,), dtype=torch.int32, device=dev)      # the last word: tiles in use
+    n_tiles = tile_expert[rows // 128:]
+    a = torch.empty((rows, K), dtype=torch.bfloat16, device=dev)
+    h = torch.empty((rows, F), dtype=torch.bfloat16, device=dev)
+    c = torch.empty((rows, Hout), dtype=torch.float32, device=dev)
+    y = torch.empty((N, Hout), dtype=torch.float32, device=dev)
+    status = tc_status_tensor(dev)
+    _lib.check(lib.gesso_moe_group_rows(_p(idx), pairs, E, _p(pair_row), _p(tile_expert), _p(n_tiles), _stream()),
+               "moe_group_rows")
+    _lib.check(lib.gesso_moe_gather_rows(_p(x), _p(pair_row), _p(a), pairs, top, K, _stream()), "moe_gather_rows")
+    _lib.check(lib.gesso_moe_gemm_tcgen05(_p(a), _p(w_up), _p(h), _p(tile_expert), _p(n_tiles), rows, E, F, K, 0,
+                                          MOE_ACTS[act], _p(status), _stream()), "moe_gemm_tcgen05 (up)")
+    _lib.check(lib.gesso_moe_gemm_tcgen05(_p(h), _p(w_down), _p(c), _p(tile_expert), _p(n_tiles), rows, E, Hout, F, 1,
+                                          0, _p(status), _stream()), "moe_gemm_tcgen05 (down)")
+    _lib.check(lib.gesso_moe_combine(_p(c), _p(pair_row), _p(w), _p(y), N, top, Hout, _stream()), "moe_combine")
+    return y
 
 
 # ---- short convolution -----------------------------------------------------------------------
@@ -318,7 +375,6 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Opti
     N = qkv.shape[0]
     vd = hd if v_head_dim is None else int(v_head_dim)
     width = (nh + nkv) * hd + nkv * vd if write_kv else nh * hd
-    plain = qkv.shape[1] == width and vd == hd and bias is None
     _need(qkv.shape[1] >= width, "fused projection width differs from the head layout")
     if bias is not None:
         _cuda_contig(bias, "bias", torch.float32)
@@ -342,14 +398,16 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Opti
     else:
         rot_dim = 0
     q_out = torch.empty((N, nh, hd), dtype=qkv.dtype, device=qkv.device)
-    full_half_split = cos is None or (rot_dim == hd and not interleaved)
-    if (tiles is not None and plain and write_kv and qkv.dtype == torch.bfloat16 and tiles[2].numel() > 0 and full_half_split
+    half_split = cos is None or (rot_dim % 8 == 0 and not interleaved)
+    if (tiles is not None and vd == hd and qkv.shape[1] % 8 == 0 and write_kv and qkv.dtype == torch.bfloat16
+            and tiles[2].numel() > 0 and half_split
             and _lib.library().gesso_qk_rope_store_tiles_takes(hd, page_size, nh, nkv)):
         seg_start, seg_pos0, tile_seg, tile_q0 = tiles
         _lib.check(_lib.library().gesso_qk_norm_rope_store_tiles(
             _p(qkv), _p(q_w), _p(k_w), float(eps), _p(cos), _p(sin), _p(seg_start), _p(seg_pos0), _p(tile_seg),
             _p(tile_q0), tile_seg.numel(), _p(block_table), block_table.shape[1], page_size, _p(q_out),
-            _p(k_pages), _p(v_pages), nh, nkv, hd, _p(status), _stream()), "qk_norm_rope_store_tiles")
+            _p(k_pages), _p(v_pages), nh, nkv, hd, _p(status), _p(bias), int(qkv.shape[1]), int(rot_dim or hd),
+            _stream()), "qk_norm_rope_store_tiles")
         return q_out
     _lib.check(_lib.library().gesso_qk_norm_rope_store(
         _p(qkv), _dt(qkv), _p(q_w), _p(k_w), float(eps), _p(cos), _p(sin), _p(positions),
@@ -677,15 +735,16 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Te
 _lib.declare("gesso_qk_rope_store_tiles_takes", [_lib.I, _lib.I, _lib.I, _lib.I])
 _lib.declare("gesso_qk_norm_rope_store_tiles", [_lib.P, _lib.P, _lib.P, _lib.F, _lib.P, _lib.P, _lib.P, _lib.P, _lib.P,
                                                 _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P, _lib.I,
-                                                _lib.I, _lib.I, _lib.P, _lib.P])
+                                                _lib.I, _lib.I, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P])
 
 # ---- tensor-core attention (bfloat16) ------------------------------------------------------------
 _lib.declare("gesso_attention_tc_takes", [_lib.I, _lib.I, _lib.I, _lib.I])
 _lib.declare("gesso_decode_attention", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P,
                                         _lib.I, _lib.I, _lib.I, _lib.I, _lib.I, _lib.F, _lib.I, _lib.P, _lib.P,
-                                        _lib.P, _lib.P, _lib.P])
+                                        _lib.P, _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.P])
 _lib.declare("gesso_prefill_attention", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P,
-                                         _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.F, _lib.P])
+                                         _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.F, _lib.I, _lib.P,
+                                         _lib.I, _lib.I, _lib.P])
 
 _lib.declare("gesso_sm_count", [])
 _sm_count = 0
@@ -705,6 +764,11 @@ def fast_attention_takes(hd: int, page_size: int, nh: int, nkv: int) -> bool:
     slots, at most 16 query heads per kv head for single-token steps."""
     return bool(_lib.library().gesso_attention_tc_takes(hd, page_size, nh, nkv)) and nh // nkv <= 16
 
+
+# Mixers that ask for attention weights of 32-bit precision get them as two bfloat16 pieces in the mma.sync
+# kernels.  GESSO_ATTN_SPLIT_WEIGHTS=0 feeds single bfloat16 weights instead (what the tcgen05 flash kernel can
+# do: its tensor memory has no room for the second piece), for measurements of that kernel on such mixers.
+ATTN_SPLIT_WEIGHTS = os.environ.get("GESSO_ATTN_SPLIT_WEIGHTS", "1") != "0"
 
 DECODE_BLOCKS_PER_SM = int(os.environ.get("GESSO_DECODE_BLOCKS_PER_SM", "2"))
 
@@ -729,13 +793,17 @@ def decode_splits(n_segs: int, nkv: int, max_kv_len: int, uneven: bool = False) 
 def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                      block_table: torch.Tensor, positions: torch.Tensor,
                      window: Optional[int], scale: float, n_splits: int,
-                     workspace=None, kv_span: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     workspace=None, kv_span: Optional[torch.Tensor] = None, keep_first: int = 0,
+                     gate: Optional[torch.Tensor] = None, split_weights: bool = False) -> torch.Tensor:
     """Split-KV attention for a step of single tokens (token i is request i).  ``workspace`` = (part_o, part_ml, tickets) of
     sizes [segs*nh*splits*hd], [segs*nh*splits*2] float32 and [segs*nkv] int32 (zeroed once).  ``kv_span``: int32 [2]
     on the device, the longest sequence of the step and the average one: a request then uses as many of the
-    ``n_splits`` pieces as the step's lengths call for (without it, all of them)."""
+    ``n_splits`` pieces as the step's lengths call for (without it, all of them).  ``keep_first``, ``gate``: as
+    for :func:`paged_attention_generic`.  ``split_weights``: the attention weights enter the product with the
+    values as two bfloat16 pieces each (16 bits of mantissa)."""
     _cuda_contig(q, "q", torch.bfloat16)
     S, nh, hd = q.shape
+    gate_stride = _check_gate(gate, S, nh * hd, q.dtype)
     nkv, page_size = k_pages.shape[1], k_pages.shape[2]
     _need(k_pages.dtype == torch.bfloat16 and v_pages.dtype == torch.bfloat16, "cache pages must be bfloat16")
     if kv_span is not None:
@@ -755,22 +823,26 @@ def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
     _lib.check(_lib.library().gesso_decode_attention(
         _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, _p(positions),
         _p(out), S, nh, nkv, hd, int(window or 0), float(scale), int(n_splits), _p(part_o),
-        _p(part_ml), _p(tickets), _p(kv_span), _stream()), "decode_attention")
+        _p(part_ml), _p(tickets), _p(kv_span), int(keep_first or 0), _p(gate), gate_stride,
+        1 if split_weights else 0, _stream()), "decode_attention")
     return out
 
 
 def prefill_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                       block_table: torch.Tensor, seg_start: torch.Tensor, seg_pos0: torch.Tensor,
                       tile_seg: torch.Tensor, tile_q0: torch.Tensor, window: Optional[int],
-                      scale: float) -> torch.Tensor:
+                      scale: float, keep_first: int = 0, gate: Optional[torch.Tensor] = None,
+                      split_weights: bool = False) -> torch.Tensor:
     _cuda_contig(q, "q", torch.bfloat16)
     N, nh, hd = q.shape
     nkv, page_size = k_pages.shape[1], k_pages.shape[2]
     out = torch.empty((N, nh * hd), dtype=q.dtype, device=q.device)
+    gate_stride = _check_gate(gate, N, nh * hd, q.dtype)
     _lib.check(_lib.library().gesso_prefill_attention(
         _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, _p(seg_start),
         _p(seg_pos0), _p(tile_seg), _p(tile_q0), tile_seg.numel(), _p(out), nh, nkv, hd, int(window or 0),
-        float(scale), _stream()), "prefill_attention")
+        float(scale), int(keep_first or 0), _p(gate), gate_stride, 1 if split_weights else 0, _stream()),
+        "prefill_attention")
     return out
 
 
@@ -909,7 +981,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, epi: int = EPI_BF16, out: Opt
 _lib.declare("gesso_attention_tcgen05_takes", [_lib.I, _lib.I, _lib.I, _lib.I])
 _lib.declare("gesso_prefill_attention_tcgen05", [_lib.P, _lib.P, _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P,
                                                  _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.I, _lib.I, _lib.I, _lib.F,
-                                                 _lib.P, _lib.P])
+                                                 _lib.P, _lib.I, _lib.P, _lib.I, _lib.P])
 
 
 def attention_tcgen05_takes(hd: int, page_size: int, nh: int, nkv: int) -> bool:
@@ -920,15 +992,18 @@ def attention_tcgen05_takes(hd: int, page_size: int, nh: int, nkv: int) -> bool:
 def prefill_attention_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                               block_table: torch.Tensor, seg_start: torch.Tensor, seg_pos0: torch.Tensor,
                               tile_seg: torch.Tensor, tile_q0: torch.Tensor, window: Optional[int],
-                              scale: float) -> torch.Tensor:
-    """Flash prefill attention on tcgen05 (S and P in tensor memory, K/V pages by TMA)."""
+                              scale: float, keep_first: int = 0, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Flash prefill attention on tcgen05 (S and P in tensor memory, K/V pages by TMA).  ``keep_first``, ``gate``:
+    as for :func:`paged_attention_generic`."""
     _cuda_contig(q, "q", torch.bfloat16)
     N, nh, hd = q.shape
+    gate_stride = _check_gate(gate, N, nh * hd, q.dtype)
     nkv, page_size = k_pages.shape[1], k_pages.shape[2]
     _need(k_pages.is_contiguous() and v_pages.is_contiguous(), "cache pages must be contiguous")
     out = torch.empty((N, nh * hd), dtype=q.dtype, device=q.device)
     _lib.check(_lib.library().gesso_prefill_attention_tcgen05(
         _p(q), _p(k_pages), _p(v_pages), k_pages.shape[0], _p(block_table), block_table.shape[1], page_size,
         _p(seg_start), _p(seg_pos0), _p(tile_seg), _p(tile_q0), tile_seg.numel(), N, _p(out), nh, nkv,
-        int(window or 0), float(scale), _p(tc_status_tensor(q.device)), _stream()), "prefill_attention_tcgen05")
+        int(window or 0), float(scale), _p(tc_status_tensor(q.device)), int(keep_first or 0), _p(gate), gate_stride,
+        _stream()), "prefill_attention_tcgen05")
     return out

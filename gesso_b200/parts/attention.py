@@ -21,7 +21,9 @@ and the cache manager keeps their pages); ``output_gate`` (a fourth projection `
 mixer's input, ``n_heads * v_head_dim`` wide: the concatenated heads are multiplied element by
 element with ``sigmoid(g)`` before the output projection; it rides in the fused matrix and the
 attention kernels apply it as they store); ``f32_output`` (the output projection's result in
-float32, for arrangements that norm it before the add).
+float32, for arrangements that norm it before the add); ``f32_weights`` (the softmax weights act
+on the values in 32-bit precision: the tensor-core kernels then feed each weight to the product
+as two bfloat16 pieces).
 """
 from __future__ import annotations
 
@@ -53,6 +55,7 @@ class GQAttention(Mixer):
         self.output_gate = bool(spec.get("output_gate", False))
         self.keep_first = int(spec.get("keep_first") or 0)
         self.f32_output = bool(spec.get("f32_output", False))
+        self.f32_weights = bool(spec.get("f32_weights", False))
         if self.vd < 1 or self.vd > 256:
             raise invalid(f"attention: v_head_dim {self.vd} must be between 1 and 256")
         if self.keep_first < 0:
@@ -134,7 +137,8 @@ class GQAttention(Mixer):
         if self.output_gate:          # the gate's columns of the fused projection, behind q (, k and v)
             g0 = (self.nh + self.nkv) * self.hd + self.nkv * self.vd if writes else self.nh * self.hd
             gate = qkv[:, g0:g0 + self.nh * self.vd]
-        o = self.rt.attention(q, cache, ctx, self.window, self.scale, keep_first=self.keep_first, gate=gate)
+        o = self.rt.attention(q, cache, ctx, self.window, self.scale, keep_first=self.keep_first, gate=gate,
+                              split_weights=self.f32_weights)
         if residual is not None:
             return ops.linear_residual(o, self.w_o, residual, None), None
         return ops.linear(o, self.w_o, out_dtype=torch.float32 if self.f32_output else x.dtype), None

@@ -14,8 +14,9 @@ and the token's output is ``sum_k weight_k * expert_k(x)`` with ``weight_k = s``
 
 Parameters (all from the part spec): hidden_size, ff_dim, n_experts, top_k, n_groups (1), keep_groups
 (= n_groups), group_top (2), score ("sigmoid"), correction (false), renormalize (false), weight_scale
-(1.0), activation ("relu2").  Tensors: ``router.weight`` [E, hidden] (float32 on the device: the router is
-32-bit whatever the run type), ``correction`` [E], ``experts.<e>.up.weight`` [ff, hidden],
+(1.0), activation ("relu2").  Tensors: ``router.weight`` [E, hidden] (the logits are a product with float32
+accumulation and a float32 result, everything after them is float32 whatever the run type), ``correction``
+[E], ``experts.<e>.up.weight`` [ff, hidden],
 ``experts.<e>.down.weight`` [hidden, ff]; the experts' matrices are stacked at bind time.
 
 Which kernels run: bfloat16 steps with more (token, expert) pairs than ``PAIR_MAX_ROWS`` group the rows by
@@ -65,7 +66,7 @@ class RoutedExperts(FeedForward):
             raise invalid(f"routed experts: unknown activation {self.act!r}; known: {sorted(ops.MOE_ACTS)}")
 
     def param_decls(self) -> Dict[str, ParamDecl]:
-        d = {"router.weight": ParamDecl((self.E, self.hidden), role="vector", fan_in=self.hidden, init="normal")}
+        d = {"router.weight": ParamDecl((self.E, self.hidden), fan_in=self.hidden)}
         if self.has_correction:
             d["correction"] = ParamDecl((self.E,), role="vector", init="zeros")
         for e in range(self.E):
