@@ -101,29 +101,40 @@ def _check() -> int:
     from .weights.random_init import write_random_model
     kernel_build.build(verbose=True)
     hostlib.build()
-    cfg = {"architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2", "vocab_size": 320, "hidden_size": 128,
-           "num_hidden_layers": 3, "num_attention_heads": 4, "num_key_value_heads": 2, "full_attn_idxs": [1],
-           "conv_L_cache": 3, "conv_bias": False, "block_ff_dim": 256, "block_auto_adjust_ff_dim": False,
-           "norm_eps": 1e-5, "rope_theta": 10000.0, "tie_embedding": True}
+    lfm2 = {"architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2", "vocab_size": 320, "hidden_size": 128,
+            "num_hidden_layers": 3, "num_attention_heads": 4, "num_key_value_heads": 2, "full_attn_idxs": [1],
+            "conv_L_cache": 3, "conv_bias": False, "block_ff_dim": 256, "block_auto_adjust_ff_dim": False,
+            "norm_eps": 1e-5, "rope_theta": 10000.0, "tie_embedding": True}
+    layer = {"type": "attention",
+             "mixer": {"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 32, "scale": 0.18,
+                       "rot": {"base": 10000.0, "dims": 16, "scaling": {"factor": 2.0}}, "mask": {"size": 12, "keep_first": 2}},
+             "mlp": {"kind": "moe", "expert": {"ff": 64}, "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}}}}
+    sodurax = {"architecture": "Sodurax", "vocab": 320, "width": 128, "norm": {"eps": 1e-6},
+               "layers": [layer, layer, dict(layer, weights_of=0)]}
     prompts = [[5, 17, 3, 250, 9, 77, 41], [1] * 19, [300]]
-    with tempfile.TemporaryDirectory() as d:
-        write_random_model(d, cfg, 0, style="fan_in")
-        for dtype, slack in (("float32", 1e-4), ("bfloat16", 0.0625)):
-            model = gesso_b200.load(d, dtype=dtype, max_positions=64)
-            s = gesso_b200.Session(model, context_length=64, max_batch=4)
-            res = s.run_batch([gesso_b200.BatchRequest(p, max_new_tokens=6) for p in prompts])
-            for p, r in zip(prompts, res):
-                if r.status != "complete":
-                    print(f"check: {dtype}: request ended as {r.status}: {r.error}", file=sys.stderr)
-                    return 1
-                whole = s.prefill(r.ids[:-1])
-                for k in range(len(p), len(r.ids)):
-                    row = whole[k - 1]
-                    if float(row.max() - row[r.ids[k]]) > slack * max(1.0, float(np.abs(row).max())):
-                        print(f"check: {dtype}: token {k} of {r.ids} is not the most likely one of a whole run",
-                              file=sys.stderr)
+    # a mixture of experts may choose another expert on a close call in bfloat16, which moves the logits by more
+    # than rounding: its decoding is held to a whole run in float32 only
+    for cfg, runs in ((lfm2, (("float32", 1e-4), ("bfloat16", 0.0625))), (sodurax, (("float32", 1e-4), ("bfloat16", None)))):
+        with tempfile.TemporaryDirectory() as d:
+            write_random_model(d, cfg, 0, style="fan_in")
+            for dtype, slack in runs:
+                model = gesso_b200.load(d, dtype=dtype, max_positions=64)
+                s = gesso_b200.Session(model, context_length=64, max_batch=4)
+                res = s.run_batch([gesso_b200.BatchRequest(p, max_new_tokens=6) for p in prompts])
+                for p, r in zip(prompts, res):
+                    if r.status != "complete":
+                        print(f"check: {dtype}: request ended as {r.status}: {r.error}", file=sys.stderr)
                         return 1
-            print(f"check: {dtype} ok")
+                    if slack is None:
+                        continue
+                    whole = s.prefill(r.ids[:-1])
+                    for k in range(len(p), len(r.ids)):
+                        row = whole[k - 1]
+                        if float(row.max() - row[r.ids[k]]) > slack * max(1.0, float(np.abs(row).max())):
+                            print(f"check: {dtype}: token {k} of {r.ids} is not the most likely one of a whole run",
+                                  file=sys.stderr)
+                            return 1
+                print(f"check: {model.spec.architecture} {dtype} ok")
     print("ok")
     return 0
 
@@ -146,8 +157,13 @@ def main(argv=None) -> int:
     if args.command == "describe":
         from .config.registry import spec_from_dir
         spec = spec_from_dir(args.model)
-        print(json.dumps({"architecture": spec.architecture, "config": getattr(spec.source, "__dict__", None),
-                          "layers": [b.mixer.kind for b in spec.blocks]}, indent=1, default=str))
+        import dataclasses
+        src = spec.source
+        config = dataclasses.asdict(src) if dataclasses.is_dataclass(src) else getattr(src, "__dict__", None)
+        if isinstance(config, dict):
+            config.pop("raw", None)          # the configuration object as it was read
+        print(json.dumps({"architecture": spec.architecture, "config": config,
+                          "layers": [spec.blocks[e.layer].mixer.kind for e in spec.schedule]}, indent=1, default=str))
         return 0
     if args.command == "check":
         return _check()
