@@ -51,6 +51,11 @@ struct __align__(1024) FaSmem {
     unsigned tmem_base;
 };
 
+// SPLIT: the attention weights act on the values with 16 bits of mantissa instead of 8.  Tensor memory has no
+// room for a second P, so a block of keys takes two rounds through the same P columns: the softmax warps write
+// bf16(p), the issuing thread adds P V into O, the warps then write bf16(p - bf16(p)) (packed pairs
+// kept in registers from the first pass) and the product is issued once more on the same values.
+template <bool SPLIT>
 __global__ void __launch_bounds__(FA_THREADS, 2)
 prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                  const __grid_constant__ CUtensorMap map_v, const int* __restrict__ block_table,
@@ -181,9 +186,11 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 dk[i] = make_desc(smem_u32(s.k[i]));
                 dv[i] = make_desc_sw32(smem_u32(s.v[i]));
             }
-            int s_next = 0, pv_next = 0;             // the next block whose scores / whose P V is to be issued
+            constexpr int R = SPLIT ? 2 : 1;         // rounds of P V per block of keys
+            int s_next = 0, pv_round = 0;            // the next block whose scores / the next round of P V to be issued
             unsigned idle = 0;
-            while (pv_next < n_blocks && ok) {
+            while (pv_round < R * n_blocks && ok) {
+                const int pv_next = pv_round / R;
                 bool progressed = false;
                 if (s_next < n_blocks && mbar_test(&s.k_full[s_next % FA_STAGES], (s_next / FA_STAGES) & 1) &&
                     (s_next == 0 || mbar_test(&s.s_free, (s_next - 1) & 1))) {
@@ -196,17 +203,17 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     ++s_next;
                     progressed = true;
                 }
-                if (pv_next < s_next && mbar_test(&s.p_ready, pv_next & 1) &&
+                if (pv_next < s_next && mbar_test(&s.p_ready, pv_round & 1) &&
                     mbar_test(&s.v_full[pv_next % FA_STAGES], (pv_next / FA_STAGES) & 1)) {
                     tc_fence_after();
                     const unsigned long long d = dv[pv_next % FA_STAGES];
 #pragma unroll
                     for (int kk = 0; kk < FA_BK / 16; ++kk)          // one V page (16 keys x 64 features, 2 KB) per step
                         umma_f16_ts(tm_o, tm_p + 8 * kk, d + kk * (16 * FA_HD * (int)sizeof(bf16) / 16), idesc_o,
-                                    (pv_next > 0 || kk > 0) ? 1u : 0u);
+                                    (pv_round > 0 || kk > 0) ? 1u : 0u);
                     umma_commit(&s.o_full);
-                    umma_commit(&s.v_empty[pv_next % FA_STAGES]);
-                    ++pv_next;
+                    if (pv_round % R == R - 1) umma_commit(&s.v_empty[pv_next % FA_STAGES]);     // the values are free after the last round
+                    ++pv_round;
                     progressed = true;
                 }
                 if (progressed) idle = 0;
@@ -263,8 +270,9 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             // (nor, therefore, on how a row's keys were cut into blocks and steps)
             const float m_blk = ceilf(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2);
             // O += P V of the block before has finished: P may be rewritten, O may be rescaled
+            constexpr int R = SPLIT ? 2 : 1;                      // rounds of P V per block
             if (j > 0) {
-                if (!wait_all(&s.o_full, (j - 1) & 1, 17)) { ok = false; break; }
+                if (!wait_all(&s.o_full, (R * j - 1) & 1, 17)) { ok = false; break; }
                 tc_fence_after();
             }
             // raise the reference maximum?  (the warp acts as one, rows that stay are scaled by 1)
@@ -289,6 +297,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             // probabilities go back to tensor memory 32 at a time as packed bfloat16
             const unsigned long long scale2 = pack_f32x2(scale_log2, scale_log2), neg_m2 = pack_f32x2(-m_use, -m_use);
             unsigned long long l2[4] = {0ull, 0ull, 0ull, 0ull};      // four chains of pairs of partial sums
+            unsigned rest[SPLIT ? FA_BK / 2 : 1];                      // what the rounding left, for the second round
 #pragma unroll
             for (int c = 0; c < FA_BK; c += 32) {
                 unsigned pk[16];
@@ -301,6 +310,10 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                     l2[(i >> 1) & 3] = add_f32x2(l2[(i >> 1) & 3], pack_f32x2(e0, e1));
                     __nv_bfloat162 b2 = __floats2bfloat162_rn(e0, e1);
                     pk[i / 2] = *reinterpret_cast<unsigned*>(&b2);
+                    if (SPLIT) {
+                        __nv_bfloat162 r2 = __floats2bfloat162_rn(e0 - __low2float(b2), e1 - __high2float(b2));
+                        rest[(c + i) / 2] = *reinterpret_cast<unsigned*>(&r2);
+                    }
                 }
                 tmem_st16(tm_p + lane_base + c / 2, pk);
             }
@@ -312,10 +325,23 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(&s.p_ready);
+            if (SPLIT) {
+                // second round: what the rounding to bfloat16 left of every probability, through the same columns
+                // once the first product has read them
+                if (!wait_all(&s.o_full, (R * j) & 1, 18)) { ok = false; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < FA_BK; c += 32)
+                    tmem_st16(tm_p + lane_base + c / 2, reinterpret_cast<unsigned(&)[16]>(rest[SPLIT ? c / 2 : 0]));
+                tmem_st_wait();
+                tc_fence_before();
+                mbar_arrive(&s.p_ready);
+            }
         }
         if (ok) {
             // the last O += P V, and out = O / l
-            if (!wait_all(&s.o_full, (n_blocks - 1) & 1, 17)) ok = false;
+            constexpr int R = SPLIT ? 2 : 1;
+            if (!wait_all(&s.o_full, (R * n_blocks - 1) & 1, 17)) ok = false;
         }
         if (ok) {
             tc_fence_after();
@@ -371,7 +397,7 @@ GESSO_API int gesso_prefill_attention_tcgen05(const void* q, const void* k_pages
                                               const int* seg_start, const int* seg_pos0, const int* tile_seg,
                                               const int* tile_q0, int n_tiles, int n_tokens, void* out, int nh, int nkv,
                                               int window, float scale, int* status, int keep, const void* gate,
-                                              int gate_stride, cudaStream_t stream) {
+                                              int gate_stride, int split, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (keep < 0 || (gate && gate_stride < nh * FA_HD)) return GESSO_ERR_BAD_SIZE;
     if (!gesso_attention_tcgen05_takes(FA_HD, page_size, nh, nkv)) return GESSO_ERR_BAD_SIZE;
@@ -412,7 +438,9 @@ GESSO_API int gesso_prefill_attention_tcgen05(const void* q, const void* k_pages
     const size_t smem = sizeof(FaSmem) + 1024;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(prefill_attention_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(prefill_attention_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem) != cudaSuccess ||
+            cudaFuncSetAttribute(prefill_attention_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem) != cudaSuccess)
             return (int)cudaGetLastError();
         configured = true;
@@ -420,8 +448,13 @@ GESSO_API int gesso_prefill_attention_tcgen05(const void* q, const void* k_pages
     const int sub = (64 + TOK - 1) / TOK;
     if ((long long)n_tiles * sub * nkv > 2147483647LL) return GESSO_ERR_BAD_SIZE;
     const dim3 grid((unsigned)(n_tiles * sub * nkv));
-    launch_pdl(prefill_attention_tcgen05_kernel, grid, dim3(FA_THREADS), smem, stream,
-        mq, mk, mv, block_table, max_pages, page_size, seg_start, seg_pos0, tile_seg, tile_q0, (bf16*)out, nh, nkv, G,
-        window, scale * FA_LOG2E, num_pages, status, keep, (const bf16*)gate, gate_stride);
+    if (split)
+        launch_pdl(prefill_attention_tcgen05_kernel<true>, grid, dim3(FA_THREADS), smem, stream,
+            mq, mk, mv, block_table, max_pages, page_size, seg_start, seg_pos0, tile_seg, tile_q0, (bf16*)out, nh, nkv, G,
+            window, scale * FA_LOG2E, num_pages, status, keep, (const bf16*)gate, gate_stride);
+    else
+        launch_pdl(prefill_attention_tcgen05_kernel<false>, grid, dim3(FA_THREADS), smem, stream,
+            mq, mk, mv, block_table, max_pages, page_size, seg_start, seg_pos0, tile_seg, tile_q0, (bf16*)out, nh, nkv, G,
+            window, scale * FA_LOG2E, num_pages, status, keep, (const bf16*)gate, gate_stride);
     return launch_status();
 }

@@ -189,6 +189,7 @@ __device__ __forceinline__ void rows_dot(const TW* __restrict__ w, size_t stride
 }
 
 #define MOE_PAIR_OUTS 32      // outputs per block (8 per warp, taken together)
+#define MOE_PAIR_MAX_SMEM (200 * 1024)     // the input row (up) or a token's activations of all its experts (down), float32
 
 template <typename TX, typename TW>
 __global__ void __launch_bounds__(128)
@@ -251,7 +252,7 @@ moe_pair_down_kernel(const TX* __restrict__ act_in, const TW* __restrict__ w_dow
 GESSO_API int gesso_moe_pair_up(const void* x, int x_dtype, const void* w_up, int w_dtype, const int* top_idx, void* act_out,
                                 int n_tokens, int top, int K, int F, int act, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (K <= 0 || F <= 0 || top < 1 || (size_t)K * sizeof(float) > 96 * 1024) return GESSO_ERR_BAD_SIZE;
+    if (K <= 0 || F <= 0 || top < 1 || (size_t)K * sizeof(float) > MOE_PAIR_MAX_SMEM) return GESSO_ERR_BAD_SIZE;
     const long long pairs = (long long)n_tokens * top;
     const int fb = (F + MOE_PAIR_OUTS - 1) / MOE_PAIR_OUTS;
     if (pairs > 2147483647LL || fb > 65535) return GESSO_ERR_BAD_SIZE;
@@ -261,8 +262,9 @@ GESSO_API int gesso_moe_pair_up(const void* x, int x_dtype, const void* w_up, in
     do {                                                                                                             \
         static size_t configured = 48 * 1024;                                                                        \
         if (smem > configured) {                                                                                     \
-            cudaFuncSetAttribute(moe_pair_up_kernel<TX, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); \
-            configured = 96 * 1024;                                                                                  \
+            cudaFuncSetAttribute(moe_pair_up_kernel<TX, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
+                                 MOE_PAIR_MAX_SMEM);                                                                 \
+            configured = MOE_PAIR_MAX_SMEM;                                                                          \
         }                                                                                                            \
         launch_pdl(moe_pair_up_kernel<TX, TW>, grid, dim3(128), smem, stream, (const TX*)x, (const TW*)w_up, top_idx, \
                    (TX*)act_out, top, K, F, act);                                                                    \
@@ -280,7 +282,7 @@ GESSO_API int gesso_moe_pair_up(const void* x, int x_dtype, const void* w_up, in
 GESSO_API int gesso_moe_pair_down(const void* act_in, int x_dtype, const void* w_down, int w_dtype, const int* top_idx,
                                   const float* top_w, float* y, int n_tokens, int top, int F, int N, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (N <= 0 || F <= 0 || top < 1 || (size_t)top * F * sizeof(float) > 96 * 1024) return GESSO_ERR_BAD_SIZE;
+    if (N <= 0 || F <= 0 || top < 1 || (size_t)top * F * sizeof(float) > MOE_PAIR_MAX_SMEM) return GESSO_ERR_BAD_SIZE;
     const int nb = (N + MOE_PAIR_OUTS - 1) / MOE_PAIR_OUTS;
     if (nb > 65535) return GESSO_ERR_BAD_SIZE;
     const dim3 grid((unsigned)n_tokens, nb);
@@ -289,8 +291,9 @@ GESSO_API int gesso_moe_pair_down(const void* act_in, int x_dtype, const void* w
     do {                                                                                                               \
         static size_t configured = 48 * 1024;                                                                          \
         if (smem > configured) {                                                                                       \
-            cudaFuncSetAttribute(moe_pair_down_kernel<TX, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); \
-            configured = 96 * 1024;                                                                                    \
+            cudaFuncSetAttribute(moe_pair_down_kernel<TX, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
+                                 MOE_PAIR_MAX_SMEM);                                                                   \
+            configured = MOE_PAIR_MAX_SMEM;                                                                            \
         }                                                                                                              \
         launch_pdl(moe_pair_down_kernel<TX, TW>, grid, dim3(128), smem, stream, (const TX*)act_in, (const TW*)w_down,  \
                    top_idx, top_w, y, top, F, N);                                                                      \

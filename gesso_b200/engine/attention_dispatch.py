@@ -4,10 +4,9 @@ float32 runs always take the FP32-arithmetic kernel.  bfloat16 runs take the ten
 when the sizes fit them (head 32/64/96/128, pages in multiples of 16 slots): the split-KV kernel
 for steps of single tokens; for steps with portions the tcgen05 flash kernel (head 64, 2 to 16 query
 heads per kv head) or else the mma.sync flash kernel; other sizes take the FP32-arithmetic kernel
-on bfloat16 data.  Kept first keys under a window and an output gate are taken by every kernel;
-attention weights in two bfloat16 pieces by the mma.sync kernels and the FP32-arithmetic kernel
-(whose weights are float32 anyway), not by the tcgen05 kernel; values of another width than the keys
-by the FP32-arithmetic kernel only.  Every
+on bfloat16 data.  Kept first keys under a window, an output gate and attention weights in two
+bfloat16 pieces are taken by every kernel (the FP32-arithmetic kernel's weights are float32 anyway);
+values of another width than the keys by the FP32-arithmetic kernel only.  Every
 branch is one of this library's own kernels.
 """
 from __future__ import annotations
@@ -39,10 +38,11 @@ def paged_attention(rt, q, cache, ctx, window, scale, keep_first: int = 0, gate=
                     rt.shared[key] = ws
             return ops.decode_attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions,
                                         window, scale, splits, ws, ctx.kv_span, keep_first, gate, split_weights)
-        if not split_weights and ops.attention_tcgen05_takes(hd, page_size, nh, nkv):
+        if ops.attention_tcgen05_takes(hd, page_size, nh, nkv):
             # head 64 with 2..16 query heads per kv head: S and P in tensor memory, pages by TMA
             return ops.prefill_attention_tcgen05(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.seg_start,
-                                                 ctx.seg_pos0, ctx.tile_seg, ctx.tile_q0, window, scale, keep_first, gate)
+                                                 ctx.seg_pos0, ctx.tile_seg, ctx.tile_q0, window, scale, keep_first, gate,
+                                                 split_weights)
         return ops.prefill_attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.seg_start,
                                      ctx.seg_pos0, ctx.tile_seg, ctx.tile_q0, window, scale, keep_first, gate,
                                      split_weights)

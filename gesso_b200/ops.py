@@ -765,9 +765,9 @@ def fast_attention_takes(hd: int, page_size: int, nh: int, nkv: int) -> bool:
     return bool(_lib.library().gesso_attention_tc_takes(hd, page_size, nh, nkv)) and nh // nkv <= 16
 
 
-# Mixers that ask for attention weights of 32-bit precision get them as two bfloat16 pieces in the mma.sync
-# kernels.  GESSO_ATTN_SPLIT_WEIGHTS=0 feeds single bfloat16 weights instead (what the tcgen05 flash kernel can
-# do: its tensor memory has no room for the second piece), for measurements of that kernel on such mixers.
+# Mixers that ask for attention weights of 32-bit precision get them as two bfloat16 pieces (a second P V
+# product per block of keys).  GESSO_ATTN_SPLIT_WEIGHTS=0 feeds single bfloat16 weights instead, to measure
+# what the second piece costs.
 ATTN_SPLIT_WEIGHTS = os.environ.get("GESSO_ATTN_SPLIT_WEIGHTS", "1") != "0"
 
 DECODE_BLOCKS_PER_SM = int(os.environ.get("GESSO_DECODE_BLOCKS_PER_SM", "2"))
@@ -981,7 +981,7 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, epi: int = EPI_BF16, out: Opt
 _lib.declare("gesso_attention_tcgen05_takes", [_lib.I, _lib.I, _lib.I, _lib.I])
 _lib.declare("gesso_prefill_attention_tcgen05", [_lib.P, _lib.P, _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P,
                                                  _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.I, _lib.I, _lib.I, _lib.F,
-                                                 _lib.P, _lib.I, _lib.P, _lib.I, _lib.P])
+                                                 _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.P])
 
 
 def attention_tcgen05_takes(hd: int, page_size: int, nh: int, nkv: int) -> bool:
@@ -992,9 +992,11 @@ def attention_tcgen05_takes(hd: int, page_size: int, nh: int, nkv: int) -> bool:
 def prefill_attention_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                               block_table: torch.Tensor, seg_start: torch.Tensor, seg_pos0: torch.Tensor,
                               tile_seg: torch.Tensor, tile_q0: torch.Tensor, window: Optional[int],
-                              scale: float, keep_first: int = 0, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                              scale: float, keep_first: int = 0, gate: Optional[torch.Tensor] = None,
+                              split_weights: bool = False) -> torch.Tensor:
     """Flash prefill attention on tcgen05 (S and P in tensor memory, K/V pages by TMA).  ``keep_first``, ``gate``:
-    as for :func:`paged_attention_generic`."""
+    as for :func:`paged_attention_generic`.  ``split_weights``: every block of keys takes two rounds of P V, the
+    weights' bfloat16 rounding and then what it left (16 bits of mantissa in all)."""
     _cuda_contig(q, "q", torch.bfloat16)
     N, nh, hd = q.shape
     gate_stride = _check_gate(gate, N, nh * hd, q.dtype)
@@ -1005,5 +1007,5 @@ def prefill_attention_tcgen05(q: torch.Tensor, k_pages: torch.Tensor, v_pages: t
         _p(q), _p(k_pages), _p(v_pages), k_pages.shape[0], _p(block_table), block_table.shape[1], page_size,
         _p(seg_start), _p(seg_pos0), _p(tile_seg), _p(tile_q0), tile_seg.numel(), N, _p(out), nh, nkv,
         int(window or 0), float(scale), _p(tc_status_tensor(q.device)), int(keep_first or 0), _p(gate), gate_stride,
-        _stream()), "prefill_attention_tcgen05")
+        1 if split_weights else 0, _stream()), "prefill_attention_tcgen05")
     return out

@@ -29,11 +29,11 @@ _B1 = _layer(3, 3, 16, 8, 0.25, {"base": 100.0, "dims": 4, "scaling": {"factor":
 SDX_B = {"architecture": "Sodurax", "vocab": 257, "width": 96, "norm": {"eps": 1e-6}, "layers": [_B0, _B1, _B0]}
 SDX_B["layers"][2] = dict(_B0, weights_of=0)
 
-# one query head per kv head, head 64, 20 kept tokens (more than a page), 16 experts in 8 pairs (5 kept), top 3;
-# the second run of the tensors has another window (parts of its own on the same tensors).
-_C = _layer(2, 2, 64, 64, 0.125, {"base": 1000.0, "dims": 8, "scaling": {"factor": 8.0}},
+# two query heads per kv head of 64 (the tcgen05 attention sizes), 20 kept tokens (more than a page), 16 experts
+# in 8 pairs (5 kept), top 3; the second run of the tensors has another window (parts of its own on the same tensors).
+_C = _layer(4, 2, 64, 64, 0.125, {"base": 1000.0, "dims": 8, "scaling": {"factor": 8.0}},
             {"size": 50, "keep_first": 20}, _moe(32, 16, 3, 8, 5))
-_C2 = _layer(2, 2, 64, 64, 0.125, {"base": 1000.0, "dims": 8, "scaling": {"factor": 8.0}},
+_C2 = _layer(4, 2, 64, 64, 0.125, {"base": 1000.0, "dims": 8, "scaling": {"factor": 8.0}},
              {"size": 33, "keep_first": 2}, _moe(32, 16, 3, 8, 5), weights_of=0)
 SDX_C = {"architecture": "Sodurax", "vocab": 300, "width": 128, "norm": {"eps": 1e-6}, "layers": [_C, _C2]}
 
