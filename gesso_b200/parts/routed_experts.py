@@ -19,7 +19,7 @@ accumulation and a float32 result, everything after them is float32 whatever the
 [E], ``experts.<e>.up.weight`` [ff, hidden],
 ``experts.<e>.down.weight`` [hidden, ff]; the experts' matrices are stacked at bind time.
 
-Which kernels run: bfloat16 steps with more (token, expert) pairs than ``PAIR_MAX_ROWS`` group the rows by
+Which kernels run: bfloat16 steps with more (token, expert) pairs than ``ops.MOE_PAIR_MAX_ROWS`` group the rows by
 expert and take the grouped tcgen05 product; fewer pairs, float32 runs and sizes that product does not take
 go pair by pair (``ops.moe_experts_pairs``).  The output is float32 (it is normed or added in 32 bit).
 """

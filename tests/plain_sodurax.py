@@ -18,10 +18,6 @@ import torch
 F64 = torch.float64
 
 
-def gelu_tanh(z):
-    return 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 def dyt(x, W, name):
     """tanh(a x) g + c."""
     return torch.tanh(W[name + ".alpha"] * x) * W[name] + W[name + ".b"]
