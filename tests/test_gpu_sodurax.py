@@ -330,7 +330,9 @@ def test_router_against_plain(E, top, groups, keep, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T,W,F,E,top", [(5, 64, 48, 8, 2), (70, 96, 40, 6, 1), (300, 128, 32, 16, 3), (33, 72, 100, 4, 4)])
+@pytest.mark.parametrize("T,W,F,E,top", [(5, 64, 48, 8, 2), (70, 96, 40, 6, 1), (300, 128, 32, 16, 3), (33, 72, 100, 4, 4),
+                                         (200, 96, 40, 6, 2), (150, 192, 64, 16, 4), (260, 200, 72, 12, 3),
+                                         (700, 512, 256, 32, 4), (129, 64, 8, 3, 1)])
 def test_experts_against_plain(T, W, F, E, top, dtype):
     """Both ways the experts run: pair by pair, and grouped by expert where the step takes that path."""
     from gesso_b200 import ops
@@ -464,6 +466,75 @@ def test_greedy_generation_through_the_session(name, loaded, plain):
     for p, r in zip(prompts, res):
         assert list(r.ids) == plain.models[name].greedy(p, 6)
     assert all(n == 0 for n in s.engine.cache.pages_in_use())
+
+
+def random_sodurax_config(seed):
+    """Seeded random configurations: head sizes the tensor-core kernels take and others, values wider or narrower than
+    keys, any grouping of heads and experts, windows shorter and longer than the prompts, layers without a
+    feed-forward, layers that borrow tensors (with the same or other constants)."""
+    import random
+    rng = random.Random(seed)
+    dim = rng.choice([16, 24, 32, 48, 64, 64, 80, 96, 128])
+    kv = rng.choice([1, 2, 3])
+    heads = kv * rng.choice([1, 2, 4])
+    vdim = dim if rng.random() < 0.7 else rng.choice([8, 16, 40, 72])
+    width = rng.choice([48, 64, 72, 96, 128, 200, 256])
+    gsz = rng.choice([1, 2, 3, 4])
+    count = rng.choice([1, 2, 3, 4, 6])
+    experts = gsz * count
+    keep = rng.randint(1, count)
+    top = rng.randint(1, min(4, gsz * keep))
+
+    def mixer():
+        rot_dims = rng.choice([d for d in (2, 4, 8, 12, 16, 24, 32, 64, dim) if d <= dim])
+        m = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": rng.choice([0.08, 0.15, dim ** -0.5]),
+             "rot": {"base": rng.choice([100.0, 1e4, 5e5]), "dims": rot_dims}, "mask": None}
+        if rng.random() < 0.7:
+            m["rot"]["scaling"] = {"factor": rng.choice([1.5, 2.0, 8.0])}
+        if rng.random() < 0.85:
+            m["mask"] = {"size": rng.choice([3, 9, 16, 17, 31, 50, 64, 200]), "keep_first": rng.choice([0, 1, 2, 5, 16, 19])}
+        return m
+
+    def mlp():
+        if rng.random() < 0.15:
+            return None
+        return {"kind": "moe", "expert": {"ff": rng.choice([8, 24, 40, 64, 100])},
+                "router": {"experts": experts, "top": top, "groups": {"count": count, "keep": keep}}}
+    layers = []
+    for i in range(rng.randint(2, 4)):
+        if i > 0 and rng.random() < 0.35:
+            src = rng.randrange(i)
+            while "weights_of" in layers[src]:
+                src = layers[src]["weights_of"]
+            L = dict(layers[src], weights_of=src)
+            if rng.random() < 0.3 and L["mixer"]["mask"]:
+                L["mixer"] = dict(L["mixer"], mask={"size": rng.choice([5, 40]), "keep_first": rng.choice([0, 3])})
+            layers.append(L)
+        else:
+            layers.append({"type": "attention", "mixer": mixer(), "mlp": mlp()})
+    cfg = {"architecture": "Sodurax", "vocab": rng.choice([97, 256, 503]), "width": width, "norm": {"eps": 1e-6}, "layers": layers}
+    return cfg, [rng.choice([1, 2, 5, 17, 33, 64, 65, 70, 97, 130]) for _ in range(4)]
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6, 7, 8, 11, 12, 29, 34])
+def test_random_configuration_replays_like_plain(seed, tmp_path):
+    import gesso_b200
+    cfg, lengths = random_sodurax_config(seed)
+    d = str(tmp_path / "model")
+    ps.write_model(d, cfg, seed)
+    plain_model = ps.PlainSodurax.from_dir(d)
+    reqs = tt.make_requests(cfg["vocab"], lengths, seed=seed)
+    ref = [plain_model.logits(t).numpy() for t in reqs]
+    margins = [plain_model.margins(t).numpy() for t in reqs]
+    for dtype in ("float32", "bfloat16"):
+        model = gesso_b200.load(d, dtype=dtype, max_positions=256)
+        for name, make in SCHEDULES.items():
+            tb, max_tokens = make(reqs)
+            out = str(tmp_path / f"{dtype}_{name}")
+            tt.run_in_process(model, tb, max_tokens, out)
+            compare(tt.read_rows(tb, out, cfg["vocab"]), ref, TOL[dtype], f"seed {seed} {name} {dtype} {cfg}",
+                    margins if dtype == "bfloat16" else None)
+        del model
 
 
 def test_trace_program_on_a_model_folder(sdx_dirs, plain, tmp_path):
