@@ -5,10 +5,11 @@ from .registry import (architecture_name, known_architectures, parse_strict_json
                        unregister_architecture)
 from .lfm2 import Lfm2Config, effective_ff_dim
 from .sodurax import SoduraxConfig
+from .memipel import MemipelConfig
 
 __all__ = [
     "BlockSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "default_schedule",
     "architecture_name", "known_architectures", "parse_strict_json", "read_config",
     "register_architecture", "spec_from_config", "spec_from_dir", "unregister_architecture",
-    "Lfm2Config", "effective_ff_dim", "SoduraxConfig",
+    "Lfm2Config", "effective_ff_dim", "SoduraxConfig", "MemipelConfig",
 ]

@@ -42,7 +42,8 @@ GESSO_API int gesso_embed_gather(const int* tokens, const void* table, int table
 // dynamic shared memory (H floats) so it is read from global memory once.
 template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__ delta,
-                                   const float* __restrict__ delta_bias, const float* __restrict__ w,
+                                   const float* __restrict__ delta_bias, const float* __restrict__ delta2,
+                                   const float* __restrict__ w,
                                    float eps, TO* __restrict__ out, const int* __restrict__ rows, int H) {
     extern __shared__ float srow[];
     __shared__ float red[33];
@@ -54,12 +55,14 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TD* __restrict__
     const int src = rows ? rows[r] : r;
     float* hrow = h + (size_t)src * H;
     const TD* drow = delta ? delta + (size_t)src * H : nullptr;
+    const float* d2row = delta2 ? delta2 + (size_t)src * H : nullptr;
     float ss = 0.f;
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
         float x = hrow[c];
         if (drow) {
             float d = to_f32(drow[c]);
             if (delta_bias) d += delta_bias[c];
+            if (d2row) d += d2row[c];
             x += d;
             if (!rows) hrow[c] = x;
         }
@@ -95,7 +98,7 @@ __device__ __forceinline__ void store4(bf16* p, float4 v) {
 template <typename TD, typename TO>
 __global__ void __launch_bounds__(NORM_VEC_THREADS)
 add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta, const float* __restrict__ delta_bias,
-                       const float* __restrict__ w, float eps, TO* __restrict__ out, const int* __restrict__ rows,
+                       const float* __restrict__ delta2, const float* __restrict__ w, float eps, TO* __restrict__ out, const int* __restrict__ rows,
                        int H) {
     __shared__ float red[33];
     // launched programmatically: let the successor be set up, then wait for what earlier kernels wrote (every
@@ -118,6 +121,10 @@ add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta, cons
                 float4 d = load4(drow + i);
                 if (delta_bias) {
                     const float4 b = load4(delta_bias + i);
+                    d.x += b.x; d.y += b.y; d.z += b.z; d.w += b.w;
+                }
+                if (delta2) {
+                    const float4 b = load4(delta2 + (size_t)src * H + i);
                     d.x += b.x; d.y += b.y; d.z += b.z; d.w += b.w;
                 }
                 a.x += d.x; a.y += d.y; a.z += d.z; a.w += d.w;
@@ -147,7 +154,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta, cons
 template <typename TD, typename TO, int VPL>
 __global__ void __launch_bounds__(NORM_WARP_ROWS * 32)
 add_rmsnorm_warp_kernel(float* __restrict__ h, const TD* __restrict__ delta, const float* __restrict__ delta_bias,
-                        const float* __restrict__ w, float eps, TO* __restrict__ out, const int* __restrict__ rows,
+                        const float* __restrict__ delta2, const float* __restrict__ w, float eps, TO* __restrict__ out, const int* __restrict__ rows,
                         int n_rows) {
     constexpr int H = VPL * 128;
     // launched programmatically: let the successor be set up, then wait for what earlier kernels wrote (every
@@ -170,6 +177,10 @@ add_rmsnorm_warp_kernel(float* __restrict__ h, const TD* __restrict__ delta, con
             float4 d = load4(drow + i);
             if (delta_bias) {
                 const float4 b = load4(delta_bias + i);
+                d.x += b.x; d.y += b.y; d.z += b.z; d.w += b.w;
+            }
+            if (delta2) {
+                const float4 b = load4(delta2 + (size_t)src * H + i);
                 d.x += b.x; d.y += b.y; d.z += b.z; d.w += b.w;
             }
             x[v].x += d.x; x[v].y += d.y; x[v].z += d.z; x[v].w += d.w;
@@ -205,11 +216,11 @@ add_rmsnorm_warp_kernel(float* __restrict__ h, const TD* __restrict__ delta, con
 }
 
 template <typename TD, typename TO>
-static bool launch_norm_warp(float* h, const void* delta, const float* delta_bias, const float* w, float eps, void* out,
+static bool launch_norm_warp(float* h, const void* delta, const float* delta_bias, const float* delta2, const float* w, float eps, void* out,
                              const int* rows, int n_rows, int H, cudaStream_t stream) {
     const int grid = (n_rows + NORM_WARP_ROWS - 1) / NORM_WARP_ROWS;
 #define WLAUNCH(VPL)                                                                                         \
-    launch_pdl(add_rmsnorm_warp_kernel<TD, TO, VPL>, dim3(grid), dim3(NORM_WARP_ROWS * 32), 0, stream, h, (const TD*)delta, delta_bias, w, \
+    launch_pdl(add_rmsnorm_warp_kernel<TD, TO, VPL>, dim3(grid), dim3(NORM_WARP_ROWS * 32), 0, stream, h, (const TD*)delta, delta_bias, delta2, w, \
                                                                                    eps, (TO*)out, rows, n_rows)
     switch (H) {
         case 512: WLAUNCH(4); return true;
@@ -222,26 +233,29 @@ static bool launch_norm_warp(float* h, const void* delta, const float* delta_bia
 #undef WLAUNCH
 }
 
+// delta2 (optional, float32 [rows of h, H], only beside a delta): a second sublayer's output that is added with
+// the first (a layer whose mixer and feed-forward both read one norm's output).
 GESSO_API int gesso_add_rmsnorm(float* h, const void* delta, int delta_dtype, const float* delta_bias,
-                                const float* w, float eps, void* out, int out_dtype, const int* rows,
+                                const float* delta2, const float* w, float eps, void* out, int out_dtype, const int* rows,
                                 int n_rows, int H, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (H <= 0 || (size_t)H * sizeof(float) > 200 * 1024) return GESSO_ERR_BAD_SIZE;
+    if (delta2 && !delta) return GESSO_ERR_UNSUPPORTED;
     if (n_rows >= 256) {      // many rows: a warp per row, for the widths it is compiled for
         bool done = false;
         if (delta_dtype == GESSO_F32 && out_dtype == GESSO_F32)
-            done = launch_norm_warp<float, float>(h, delta, delta_bias, w, eps, out, rows, n_rows, H, stream);
+            done = launch_norm_warp<float, float>(h, delta, delta_bias, delta2, w, eps, out, rows, n_rows, H, stream);
         else if (delta_dtype == GESSO_BF16 && out_dtype == GESSO_BF16)
-            done = launch_norm_warp<bf16, bf16>(h, delta, delta_bias, w, eps, out, rows, n_rows, H, stream);
+            done = launch_norm_warp<bf16, bf16>(h, delta, delta_bias, delta2, w, eps, out, rows, n_rows, H, stream);
         else if (delta_dtype == GESSO_F32 && out_dtype == GESSO_BF16)
-            done = launch_norm_warp<float, bf16>(h, delta, delta_bias, w, eps, out, rows, n_rows, H, stream);
+            done = launch_norm_warp<float, bf16>(h, delta, delta_bias, delta2, w, eps, out, rows, n_rows, H, stream);
         else if (delta_dtype == GESSO_BF16 && out_dtype == GESSO_F32)
-            done = launch_norm_warp<bf16, float>(h, delta, delta_bias, w, eps, out, rows, n_rows, H, stream);
+            done = launch_norm_warp<bf16, float>(h, delta, delta_bias, delta2, w, eps, out, rows, n_rows, H, stream);
         if (done) return launch_status();
     }
     if (H % 4 == 0 && H <= 4 * NORM_VEC_THREADS * NORM_VEC_MAX) {
 #define VLAUNCH(TD, TO)                                                                             \
-    launch_pdl(add_rmsnorm_vec_kernel<TD, TO>, dim3(n_rows), dim3(NORM_VEC_THREADS), 0, stream, h, (const TD*)delta, delta_bias, w, eps, \
+    launch_pdl(add_rmsnorm_vec_kernel<TD, TO>, dim3(n_rows), dim3(NORM_VEC_THREADS), 0, stream, h, (const TD*)delta, delta_bias, delta2, w, eps, \
                                                                              (TO*)out, rows, H)
         if (delta_dtype == GESSO_F32 && out_dtype == GESSO_F32) VLAUNCH(float, float);
         else if (delta_dtype == GESSO_BF16 && out_dtype == GESSO_BF16) VLAUNCH(bf16, bf16);
@@ -260,7 +274,7 @@ GESSO_API int gesso_add_rmsnorm(float* h, const void* delta, int delta_dtype, co
             cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                  (int)smem);                                                        \
         launch_pdl(add_rmsnorm_kernel<TD, TO>, dim3(n_rows), dim3(threads), smem, stream,           \
-            h, (const TD*)delta, delta_bias, w, eps, (TO*)out, rows, H);                            \
+            h, (const TD*)delta, delta_bias, delta2, w, eps, (TO*)out, rows, H);                            \
     } while (0)
     if (delta_dtype == GESSO_F32 && out_dtype == GESSO_F32) LAUNCH(float, float);
     else if (delta_dtype == GESSO_BF16 && out_dtype == GESSO_BF16) LAUNCH(bf16, bf16);

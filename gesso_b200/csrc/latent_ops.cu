@@ -1,0 +1,131 @@
+// Pieces of latent attention (queries and keys/values that go through a low-rank latent).
+//
+// 1. latent_norm_store: the fused down projection's rows p [N, Rq + Rkv] (float32 sums of a matrix product): the
+//    first Rq columns are the query latent, the next Rkv the key/value latent.  Each piece is divided by its own
+//    root mean square (eps inside the root) and scaled by its weight, in float32.  The query latent goes to
+//    cq [N, Rq] (the operand of the up projection); the key/value latent c is the ONLY thing a position leaves in
+//    the cache: it is written to the position's slot of the K pages ([page][1][slot][Rkv]).  Either piece may be
+//    absent (Rq = 0: queries without a latent; write_kv = 0: an entry that reads another entry's cache).
+//    One warp per token.
+//
+// 2. headwise_linear: out[n, h, o] = sum_i W[h, i, o] x[n, h, i] for per-head matrices W [H, I, O] (input-major, so
+//    that the threads of a block, one per output, read neighbouring elements).  Latent
+//    attention in its absorbed form uses it twice: the query of head h is carried into the latent space,
+//    q'[h] = W_uk[h]^T q[h] (so that scores are q' . c against the cached latent itself), and the weighted sum of
+//    latents is carried out of it, o[h] = W_uv[h] (sum_j p_j c_j).  float32 accumulation; x, W and out each
+//    float32 or bfloat16.  A block takes 4 rows x 1 head x 128 outputs; x rows sit in shared memory.
+#include "common.cuh"
+
+template <typename TO>
+__global__ void __launch_bounds__(128)
+latent_norm_store_kernel(const float* __restrict__ p, int Rq, int Rkv, const float* __restrict__ wq,
+                         const float* __restrict__ wkv, float eps, TO* __restrict__ cq,
+                         const int* __restrict__ positions, const int* __restrict__ seg_of_token,
+                         const int* __restrict__ block_table, int max_pages, int page_size,
+                         TO* __restrict__ k_pages, int write_kv, int* __restrict__ status, int n_tokens) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (t >= n_tokens) return;
+    const float* row = p + (size_t)t * (Rq + Rkv);
+    if (Rq > 0) {
+        float ss = 0.f;
+        for (int j = lane; j < Rq; j += 32) ss += row[j] * row[j];
+        ss = warp_sum(ss);
+        const float denom = sqrtf(ss / (float)Rq + eps);
+        for (int j = lane; j < Rq; j += 32) cq[(size_t)t * Rq + j] = from_f32<TO>((row[j] / denom) * wq[j]);
+    }
+    if (write_kv && Rkv > 0) {
+        const float* r2 = row + Rq;
+        float ss = 0.f;
+        for (int j = lane; j < Rkv; j += 32) ss += r2[j] * r2[j];
+        ss = warp_sum(ss);
+        const float denom = sqrtf(ss / (float)Rkv + eps);
+        const int pos = positions[t];
+        const int page = block_table[(size_t)seg_of_token[t] * max_pages + pos / page_size];
+        if (page < 0) {
+            if (lane == 0) atomicExch(status, 1);
+            return;
+        }
+        TO* dst = k_pages + ((size_t)page * page_size + (pos % page_size)) * Rkv;
+        for (int j = lane; j < Rkv; j += 32) dst[j] = from_f32<TO>((r2[j] / denom) * wkv[j]);
+    }
+}
+
+GESSO_API int gesso_latent_norm_store(const float* p, int Rq, int Rkv, const float* wq, const float* wkv, float eps,
+                                      void* cq, int dtype, const int* positions, const int* seg_of_token,
+                                      const int* block_table, int max_pages, int page_size, void* k_pages,
+                                      int write_kv, int* status, int n_tokens, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (Rq < 0 || Rkv < 0 || Rq + Rkv <= 0 || page_size <= 0) return GESSO_ERR_BAD_SIZE;
+    const dim3 grid((n_tokens + 3) / 4);
+    if (dtype == GESSO_F32)
+        launch_pdl(latent_norm_store_kernel<float>, grid, dim3(128), 0, stream, p, Rq, Rkv, wq, wkv, eps, (float*)cq,
+                   positions, seg_of_token, block_table, max_pages, page_size, (float*)k_pages, write_kv, status, n_tokens);
+    else if (dtype == GESSO_BF16)
+        launch_pdl(latent_norm_store_kernel<bf16>, grid, dim3(128), 0, stream, p, Rq, Rkv, wq, wkv, eps, (bf16*)cq,
+                   positions, seg_of_token, block_table, max_pages, page_size, (bf16*)k_pages, write_kv, status, n_tokens);
+    else
+        return GESSO_ERR_BAD_DTYPE;
+    return launch_status();
+}
+
+// ---- per-head matrices ----------------------------------------------------------------------------------------
+#define HW_ROWS 4
+#define HW_OUTS 128
+
+template <typename TX, typename TW, typename TO>
+__global__ void __launch_bounds__(HW_OUTS)
+headwise_linear_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TO* __restrict__ out, int n_rows, int H,
+                       int I, int O) {
+    extern __shared__ float hw_x[];          // [HW_ROWS][I]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int h = blockIdx.y, r0 = blockIdx.x * HW_ROWS, o = blockIdx.z * HW_OUTS + threadIdx.x;
+    for (int j = threadIdx.x; j < HW_ROWS * I; j += HW_OUTS) {
+        const int r = r0 + j / I;
+        hw_x[j] = r < n_rows ? to_f32(x[((size_t)r * H + h) * I + (j % I)]) : 0.f;
+    }
+    __syncthreads();
+    if (o >= O) return;
+    const TW* wr = w + (size_t)h * I * O + o;
+    float acc[HW_ROWS];
+#pragma unroll
+    for (int r = 0; r < HW_ROWS; ++r) acc[r] = 0.f;
+    for (int i = 0; i < I; ++i) {
+        const float wv = to_f32(wr[(size_t)i * O]);
+#pragma unroll
+        for (int r = 0; r < HW_ROWS; ++r) acc[r] += wv * hw_x[r * I + i];
+    }
+#pragma unroll
+    for (int r = 0; r < HW_ROWS; ++r)
+        if (r0 + r < n_rows) out[((size_t)(r0 + r) * H + h) * O + o] = from_f32<TO>(acc[r]);
+}
+
+// x [n_rows, H, I], w [H, I, O], out [n_rows, H, O]; dtypes each GESSO_F32 or GESSO_BF16.
+GESSO_API int gesso_headwise_linear(const void* x, int x_dtype, const void* w, int w_dtype, void* out, int out_dtype,
+                                    int n_rows, int H, int I, int O, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (H <= 0 || I <= 0 || O <= 0 || H > 65535 || (O + HW_OUTS - 1) / HW_OUTS > 65535) return GESSO_ERR_BAD_SIZE;
+    const size_t smem = (size_t)HW_ROWS * I * sizeof(float);
+    if (smem > 48 * 1024) return GESSO_ERR_BAD_SIZE;
+    const dim3 grid((n_rows + HW_ROWS - 1) / HW_ROWS, H, (O + HW_OUTS - 1) / HW_OUTS);
+#define GO(TX, TW, TO)                                                                                             \
+    launch_pdl(headwise_linear_kernel<TX, TW, TO>, grid, dim3(HW_OUTS), smem, stream, (const TX*)x, (const TW*)w,  \
+               (TO*)out, n_rows, H, I, O)
+    const int key = x_dtype * 4 + w_dtype * 2 + out_dtype;
+    switch (key) {
+        case 0: GO(float, float, float); break;
+        case 1: GO(float, float, bf16); break;
+        case 2: GO(float, bf16, float); break;
+        case 3: GO(float, bf16, bf16); break;
+        case 4: GO(bf16, float, float); break;
+        case 5: GO(bf16, float, bf16); break;
+        case 6: GO(bf16, bf16, float); break;
+        case 7: GO(bf16, bf16, bf16); break;
+        default: return GESSO_ERR_BAD_DTYPE;
+    }
+#undef GO
+    return launch_status();
+}

@@ -25,18 +25,25 @@ LL = c_longlong
 # name -> argtypes (the CUDA stream is always the last argument)
 _SIGNATURES = {
     "gesso_embed_gather": [P, P, I, P, I, I, I, F, P],
-    "gesso_add_rmsnorm": [P, P, I, P, P, F, P, I, P, I, I, P],
+    "gesso_add_rmsnorm": [P, P, I, P, P, P, F, P, I, P, I, I, P],
     "gesso_rmsnorm_rows": [P, P, F, P, I, I, I, P],
     "gesso_short_conv": [P, I, P, P, P, P, LL, P, P, P, P, P, I, I, I, I, I, I, P],
     "gesso_skinny_conv_takes": [I, I, I, I],
     "gesso_skinny_gemm_conv": [P, P, P, F, P, P, I, I, I, P, P, P, P, LL, P, P, I, P],
     "gesso_qk_norm_rope_store": [P, I, P, P, F, P, P, P, P, P, I, I, P, P, P, I, I, I, I, I, I, I, P, P, I, I, P],
-    "gesso_paged_attention_generic": [P, P, P, I, P, I, I, P, P, P, I, I, I, I, I, F, I, I, P, I, P],
+    "gesso_paged_attention_generic": [P, P, P, I, P, I, I, P, P, P, I, I, I, I, I, F, I, I, P, I, I, P, P, I, P],
     "gesso_add_dyt": [P, P, I, P, F, P, P, F, P, P, P, I, P, I, I, P],
     "gesso_moe_route": [P, P, P, P, I, I, I, I, I, I, I, I, F, P],
-    "gesso_moe_pair_up": [P, I, P, I, P, P, I, I, I, I, I, P],
-    "gesso_moe_pair_down": [P, I, P, I, P, P, P, I, I, I, I, P],
+    "gesso_moe_pair_up": [P, I, P, I, P, P, I, I, I, I, I, F, I, P],
+    "gesso_moe_pair_down": [P, I, P, I, P, P, P, I, I, I, I, I, P],
     "gesso_swiglu": [P, P, I, I, I, I, P],
+    "gesso_gelu_erf": [P, P, I, LL, P],
+    "gesso_glu_clamped": [P, P, I, I, I, I, F, F, P],
+    "gesso_causal_conv": [P, I, I, P, P, P, LL, P, P, P, P, I, I, I, I, P, I, I, I, F, P],
+    "gesso_latent_norm_store": [P, I, I, P, P, F, P, I, P, P, P, I, I, P, I, P, I, P],
+    "gesso_headwise_linear": [P, I, P, I, P, I, I, I, I, I, P],
+    "gesso_lightning": [P, I, I, P, LL, P, P, P, P, I, I, I, I, I, P],
+    "gesso_gated_rmsnorm": [P, P, F, P, I, P, I, I, I, P],
     "gesso_skinny_gemm_takes": [I, I, I],
     "gesso_skinny_gemm": [P, P, P, F, P, P, P, I, I, I, I, P, LL, P],
     "gesso_gemm_f32": [P, I, P, I, P, P, I, I, I, P],

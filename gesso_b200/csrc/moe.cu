@@ -17,12 +17,19 @@
 // per pair and 32 outputs, a warp per output, 16-byte weight reads), `moe_pair_down` computes
 // y[token] = sum_k weight_k * (W_down[e_k] act[token, k]) in the order of the choice (a block per token and
 // 32 outputs).  Weights of all experts are stacked: W_up [E, F, K], W_down [E, N, F].
+//
+// A gated activation (`MOE_ACT_GLU_CLAMPED`: g = min(gate, limit), u = clamp(up, -limit, limit),
+// act = g * sigmoid(1.702 g) * (u + 1)) takes W_up [E, 2F, K] with an expert's gate and up rows together: groups
+// of 8 gate rows followed by their 8 up rows (`glu_packed`, F % 8 == 0), or all F gate rows and then all F up rows;
+// a warp then computes the eight gate rows and the eight up rows of its outputs.  `moe_pair_down` with
+// `accumulate` adds its sums to what y holds (a shared expert's output, say).
 #include <math.h>
 
 #include "common.cuh"
 
 enum { MOE_SCORE_SIGMOID = 0, MOE_SCORE_SOFTMAX = 1 };
-enum { MOE_ACT_RELU2 = 0, MOE_ACT_SILU = 1, MOE_ACT_GELU_TANH = 2 };
+enum { MOE_ACT_RELU2 = 0, MOE_ACT_SILU = 1, MOE_ACT_GELU_TANH = 2, MOE_ACT_GLU_CLAMPED = 3 };
+#define MOE_GLU_ALPHA 1.702f
 
 __device__ __forceinline__ float moe_act(float v, int act) {
     if (act == MOE_ACT_RELU2) { const float r = fmaxf(v, 0.f); return r * r; }
@@ -194,7 +201,7 @@ __device__ __forceinline__ void rows_dot(const TW* __restrict__ w, size_t stride
 template <typename TX, typename TW>
 __global__ void __launch_bounds__(128)
 moe_pair_up_kernel(const TX* __restrict__ x, const TW* __restrict__ w_up, const int* __restrict__ top_idx,
-                   TX* __restrict__ act_out, int top, int K, int F, int act) {
+                   TX* __restrict__ act_out, int top, int K, int F, int act, float limit, int glu_packed) {
     extern __shared__ float moe_smem[];
     const int pair = blockIdx.x, f0 = blockIdx.y * MOE_PAIR_OUTS;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
@@ -208,6 +215,22 @@ moe_pair_up_kernel(const TX* __restrict__ x, const TW* __restrict__ w_up, const 
     if (f >= F) return;
     const int n_rows = min(8, F - f);
     float v[8];
+    if (act == MOE_ACT_GLU_CLAMPED) {
+        // the expert's 2F rows: gate rows of outputs f .. f+7, and their up rows 8 (packed) or F rows further on
+        const TW* wg = w_up + ((size_t)e * 2 * F + (glu_packed ? 2 * f : f)) * K;
+        float u[8];
+        rows_dot<TW, 8>(wg, (size_t)K, n_rows, moe_smem, K, lane, v);
+        rows_dot<TW, 8>(wg + (size_t)(glu_packed ? 8 : F) * K, (size_t)K, n_rows, moe_smem, K, lane, u);
+        if (lane < n_rows) {
+            float g = v[0], up = u[0];
+#pragma unroll
+            for (int r = 1; r < 8; ++r) { g = lane == r ? v[r] : g; up = lane == r ? u[r] : up; }
+            g = fminf(g, limit);
+            up = fminf(fmaxf(up, -limit), limit);
+            act_out[(size_t)pair * F + f + lane] = from_f32<TX>((g / (1.f + expf(-MOE_GLU_ALPHA * g))) * (up + 1.f));
+        }
+        return;
+    }
     rows_dot<TW, 8>(w_up + ((size_t)e * F + f) * K, (size_t)K, n_rows, moe_smem, K, lane, v);
     if (lane < n_rows) {
         float mine = v[0];
@@ -220,7 +243,7 @@ moe_pair_up_kernel(const TX* __restrict__ x, const TW* __restrict__ w_up, const 
 template <typename TX, typename TW>
 __global__ void __launch_bounds__(128)
 moe_pair_down_kernel(const TX* __restrict__ act_in, const TW* __restrict__ w_down, const int* __restrict__ top_idx,
-                     const float* __restrict__ top_w, float* __restrict__ y, int top, int F, int N) {
+                     const float* __restrict__ top_w, float* __restrict__ y, int top, int F, int N, int accumulate) {
     extern __shared__ float moe_smem[];
     const int tok = blockIdx.x, n0 = blockIdx.y * MOE_PAIR_OUTS;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
@@ -244,15 +267,18 @@ moe_pair_down_kernel(const TX* __restrict__ act_in, const TW* __restrict__ w_dow
         float mine = sum[0];
 #pragma unroll
         for (int r = 1; r < 8; ++r) mine = lane == r ? sum[r] : mine;
-        y[(size_t)tok * N + n + lane] = mine;
+        float* dst = y + (size_t)tok * N + n + lane;
+        *dst = accumulate ? *dst + mine : mine;
     }
 }
 
 // x [tokens, K] and act [tokens * top, F] of x_dtype; w_up [E, F, K] of w_dtype.
 GESSO_API int gesso_moe_pair_up(const void* x, int x_dtype, const void* w_up, int w_dtype, const int* top_idx, void* act_out,
-                                int n_tokens, int top, int K, int F, int act, cudaStream_t stream) {
+                                int n_tokens, int top, int K, int F, int act, float limit, int glu_packed,
+                                cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (K <= 0 || F <= 0 || top < 1 || (size_t)K * sizeof(float) > MOE_PAIR_MAX_SMEM) return GESSO_ERR_BAD_SIZE;
+    if (act == MOE_ACT_GLU_CLAMPED && glu_packed && F % 8 != 0) return GESSO_ERR_BAD_SIZE;
     const long long pairs = (long long)n_tokens * top;
     const int fb = (F + MOE_PAIR_OUTS - 1) / MOE_PAIR_OUTS;
     if (pairs > 2147483647LL || fb > 65535) return GESSO_ERR_BAD_SIZE;
@@ -267,7 +293,7 @@ GESSO_API int gesso_moe_pair_up(const void* x, int x_dtype, const void* w_up, in
             configured = MOE_PAIR_MAX_SMEM;                                                                          \
         }                                                                                                            \
         launch_pdl(moe_pair_up_kernel<TX, TW>, grid, dim3(128), smem, stream, (const TX*)x, (const TW*)w_up, top_idx, \
-                   (TX*)act_out, top, K, F, act);                                                                    \
+                   (TX*)act_out, top, K, F, act, limit, glu_packed);                                                                  \
     } while (0)
     if (x_dtype == GESSO_F32 && w_dtype == GESSO_F32) GO(float, float);
     else if (x_dtype == GESSO_F32 && w_dtype == GESSO_BF16) GO(float, bf16);
@@ -280,7 +306,8 @@ GESSO_API int gesso_moe_pair_up(const void* x, int x_dtype, const void* w_up, in
 
 // act [tokens * top, F] of x_dtype; w_down [E, N, F] of w_dtype; y [tokens, N] float32.
 GESSO_API int gesso_moe_pair_down(const void* act_in, int x_dtype, const void* w_down, int w_dtype, const int* top_idx,
-                                  const float* top_w, float* y, int n_tokens, int top, int F, int N, cudaStream_t stream) {
+                                  const float* top_w, float* y, int n_tokens, int top, int F, int N, int accumulate,
+                                  cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (N <= 0 || F <= 0 || top < 1 || (size_t)top * F * sizeof(float) > MOE_PAIR_MAX_SMEM) return GESSO_ERR_BAD_SIZE;
     const int nb = (N + MOE_PAIR_OUTS - 1) / MOE_PAIR_OUTS;
@@ -296,7 +323,7 @@ GESSO_API int gesso_moe_pair_down(const void* act_in, int x_dtype, const void* w
             configured = MOE_PAIR_MAX_SMEM;                                                                            \
         }                                                                                                              \
         launch_pdl(moe_pair_down_kernel<TX, TW>, grid, dim3(128), smem, stream, (const TX*)act_in, (const TW*)w_down,  \
-                   top_idx, top_w, y, top, F, N);                                                                      \
+                   top_idx, top_w, y, top, F, N, accumulate);                                                                    \
     } while (0)
     if (x_dtype == GESSO_F32 && w_dtype == GESSO_F32) GO(float, float);
     else if (x_dtype == GESSO_F32 && w_dtype == GESSO_BF16) GO(float, bf16);

@@ -27,8 +27,35 @@
 #define MG_BK 64
 #define MG_THREADS 192
 
-enum { MG_EPI_ACT_BF16 = 0, MG_EPI_F32 = 1 };
+enum { MG_EPI_ACT_BF16 = 0, MG_EPI_F32 = 1, MG_EPI_GLU_BF16 = 2 };
 enum { MG_ACT_RELU2 = 0, MG_ACT_SILU = 1, MG_ACT_GELU_TANH = 2 };
+#define MG_GLU_ALPHA 1.702f
+
+// A gated unit with clamped inputs on packed columns (8 gate columns, then their 8 up columns): 32 accumulator
+// columns give 16 outputs, g * sigmoid(1.702 g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit);
+// the output row is N / 2 wide.
+__device__ __forceinline__ void mg_store_glu(const unsigned (&r)[32], void* __restrict__ out, int row, int col, int N,
+                                             float limit) {
+    bf16* o = reinterpret_cast<bf16*>(out) + (size_t)row * (N / 2) + col / 2;
+#pragma unroll
+    for (int grp = 0; grp < 2; ++grp) {
+        if (col + grp * 16 >= N) break;
+        unsigned pk[4];
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+            float y[2];
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const float g = fminf(__uint_as_float(r[grp * 16 + i + k]), limit);
+                const float u = fminf(fmaxf(__uint_as_float(r[grp * 16 + 8 + i + k]), -limit), limit);
+                y[k] = (g / (1.f + expf(-MG_GLU_ALPHA * g))) * (u + 1.f);
+            }
+            __nv_bfloat162 v = __floats2bfloat162_rn(y[0], y[1]);
+            pk[i / 2] = *reinterpret_cast<unsigned*>(&v);
+        }
+        *reinterpret_cast<uint4*>(o + grp * 8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    }
+}
 
 __device__ __forceinline__ float mg_act(float v, int act) {
     if (act == MG_ACT_RELU2) { const float r = fmaxf(v, 0.f); return r * r; }
@@ -86,14 +113,14 @@ moe_gather_rows_kernel(const bf16* __restrict__ x, const int* __restrict__ pair_
 // ---- 4. weighted sum of a token's experts ---------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* __restrict__ c, const int* __restrict__ pair_row, const float* __restrict__ top_w,
-                   float* __restrict__ y, int n_tokens, int top, int N) {
+                   float* __restrict__ y, int n_tokens, int top, int N, int accumulate) {
     pdl_launch_dependents();
     pdl_wait();
     const int per_row = N / 4;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (long long)n_tokens * per_row) return;
     const int t = (int)(idx / per_row), j = (int)(idx % per_row) * 4;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 acc = accumulate ? *reinterpret_cast<const float4*>(y + (size_t)t * N + j) : make_float4(0.f, 0.f, 0.f, 0.f);
     // eight experts at a time: their rows are looked up and requested together, then added in the order of the choice
     for (int k0 = 0; k0 < top; k0 += 8) {
         int row[8];
@@ -129,7 +156,7 @@ template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(MG_THREADS, 1)
 moe_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                         void* __restrict__ out, const int* __restrict__ tile_expert, const int* __restrict__ n_row_tiles,
-                        int N, int K, int act, int* __restrict__ status) {
+                        int N, int K, int act, float limit, int* __restrict__ status) {
     extern __shared__ unsigned char smem_raw[];
     MgSmem<BN, STAGES>& s = *reinterpret_cast<MgSmem<BN, STAGES>*>(((size_t)smem_raw + 1023) & ~(size_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -224,7 +251,9 @@ moe_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
                 tmem_ld_wait();
                 const int col = n0 + c;
                 if (col >= N) continue;
-                if (EPI == MG_EPI_ACT_BF16) {
+                if (EPI == MG_EPI_GLU_BF16) {
+                    mg_store_glu(r, out, row, col, N, limit);
+                } else if (EPI == MG_EPI_ACT_BF16) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(mg_act(__uint_as_float(r[i]), act));
                     tc_store_32<TC_EPI_BF16>(r, out, nullptr, row, col, N);
@@ -278,20 +307,21 @@ GESSO_API int gesso_moe_gather_rows(const void* x, const int* pair_row, void* a,
     return launch_status();
 }
 
+// accumulate: the sums are added to what y holds (a shared expert's output, say)
 GESSO_API int gesso_moe_combine(const float* c, const int* pair_row, const float* top_w, float* y, int n_tokens, int top,
-                                int N, cudaStream_t stream) {
+                                int N, int accumulate, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (N % 4 != 0) return GESSO_ERR_BAD_SIZE;
     const long long total = (long long)n_tokens * (N / 4);
     const long long blocks = (total + 255) / 256;
     if (blocks > 2147483647LL) return GESSO_ERR_BAD_SIZE;
-    launch_pdl(moe_combine_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, c, pair_row, top_w, y, n_tokens, top, N);
+    launch_pdl(moe_combine_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, c, pair_row, top_w, y, n_tokens, top, N, accumulate);
     return launch_status();
 }
 
 template <int BN, int STAGES, int EPI>
 static int launch_mg(const CUtensorMap& ma, const CUtensorMap& mw, void* out, const int* tile_expert, const int* n_row_tiles,
-                     int max_row_tiles, int N, int K, int act, int* status, cudaStream_t stream) {
+                     int max_row_tiles, int N, int K, int act, float limit, int* status, cudaStream_t stream) {
     const size_t smem = sizeof(MgSmem<BN, STAGES>) + 1024;
     static bool configured = false;
     if (!configured) {
@@ -304,18 +334,20 @@ static int launch_mg(const CUtensorMap& ma, const CUtensorMap& mw, void* out, co
     const int sms = gesso_sm_count();
     const dim3 grid((unsigned)(tiles < sms ? tiles : sms));
     launch_pdl(moe_gemm_tcgen05_kernel<BN, STAGES, EPI>, grid, dim3(MG_THREADS), smem, stream, ma, mw, out, tile_expert,
-               n_row_tiles, N, K, act, status);
+               n_row_tiles, N, K, act, limit, status);
     return launch_status();
 }
 
 // A: bfloat16 [rows_cap, K] (rows by expert, see moe_group_rows); W: bfloat16 [E, N, K]; out: [rows_cap, N],
-// bfloat16 act(C) for epi 0, float32 C for epi 1.  tile_expert / n_row_tiles: from moe_group_rows, on the device.
+// bfloat16 act(C) for epi 0, float32 C for epi 1; epi 2: bfloat16 [rows_cap, N / 2], the clamped gated unit on
+// packed gate/up columns (N % 16 == 0).  tile_expert / n_row_tiles: from moe_group_rows, on the device.
 GESSO_API int gesso_moe_gemm_tcgen05(const void* A, const void* W, void* out, const int* tile_expert,
                                      const int* n_row_tiles, long long rows_cap, int E, int N, int K, int epi, int act,
-                                     int* status, cudaStream_t stream) {
+                                     float limit, int* status, cudaStream_t stream) {
     if (rows_cap <= 0) return 0;
     if (rows_cap % MG_BM != 0 || rows_cap > 2147483647LL || (long long)E * N > 2147483647LL) return GESSO_ERR_BAD_SIZE;
     if (N < 8 || N % 8 != 0 || K < 8 || K % 8 != 0) return GESSO_ERR_BAD_SIZE;
+    if (epi == MG_EPI_GLU_BF16 && N % 16 != 0) return GESSO_ERR_BAD_SIZE;
     if (((size_t)A & 15) || ((size_t)W & 15) || ((size_t)out & 15)) return GESSO_ERR_BAD_SIZE;
     const bool wide = N % 256 == 0 || N >= 1024;
     CUtensorMap ma, mw;
@@ -328,10 +360,13 @@ GESSO_API int gesso_moe_gemm_tcgen05(const void* A, const void* W, void* out, co
     switch (epi) {                                                                                                      \
         case MG_EPI_ACT_BF16:                                                                                           \
             return launch_mg<BN, ST, MG_EPI_ACT_BF16>(ma, mw, out, tile_expert, n_row_tiles, max_row_tiles, N, K, act,  \
-                                                      status, stream);                                                  \
+                                                      limit, status, stream);                                           \
         case MG_EPI_F32:                                                                                                \
             return launch_mg<BN, ST, MG_EPI_F32>(ma, mw, out, tile_expert, n_row_tiles, max_row_tiles, N, K, act,       \
-                                                 status, stream);                                                       \
+                                                 limit, status, stream);                                                \
+        case MG_EPI_GLU_BF16:                                                                                           \
+            return launch_mg<BN, ST, MG_EPI_GLU_BF16>(ma, mw, out, tile_expert, n_row_tiles, max_row_tiles, N, K, act,  \
+                                                      limit, status, stream);                                           \
         default: return GESSO_ERR_UNSUPPORTED;                                                                          \
     }
     if (wide) { GO(256, 4) } else { GO(128, 4) }

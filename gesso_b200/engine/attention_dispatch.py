@@ -16,9 +16,16 @@ import torch
 from .. import ops
 
 
-def paged_attention(rt, q, cache, ctx, window, scale, keep_first: int = 0, gate=None, split_weights: bool = False):
+def paged_attention(rt, q, cache, ctx, window, scale, keep_first: int = 0, gate=None, split_weights: bool = False,
+                    sink=None, slopes=None, values_are_keys: bool = False):
     N, nh, hd = q.shape
     nkv, page_size = cache.k_pages.shape[1], cache.k_pages.shape[2]
+    if sink is not None or slopes is not None or values_are_keys:
+        # a sink in the denominator, a distance bias on the scores, values that are the keys themselves
+        # (latent attention, absorbed) or float32 queries: the FP32-arithmetic kernel takes them all
+        return ops.paged_attention_generic(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions,
+                                           ctx.seg_of_token, window, scale, keep_first if window is not None else 0,
+                                           gate, sink=sink, slopes=slopes, values_are_keys=values_are_keys)
     vd = cache.v_pages.shape[2]
     if window is None:
         keep_first = 0                       # without a window every earlier key is visible anyway

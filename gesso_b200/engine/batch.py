@@ -138,6 +138,8 @@ class StepContext:
             buf[o[f"block_table{g}"]:o[f"block_table{g}"] + S * layout.max_pages].view(S, layout.max_pages)
             for g in range(layout.n_groups)]
         self.extra = {name: buf[o[name]:o[name] + sizes[name]] for name in _EXTRA_FIELDS}
+        # what a layer leaves for later layers of the same step (emptied at the start of every forward pass)
+        self.shared: Dict = {}
 
     @property
     def decode_only(self) -> bool:

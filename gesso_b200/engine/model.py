@@ -37,10 +37,12 @@ class Runtime:
         self.max_positions = int(max_positions)
         self.shared: Dict = {}
 
-    def attention(self, q, cache, ctx, window, scale, keep_first: int = 0, gate=None, split_weights: bool = False):
+    def attention(self, q, cache, ctx, window, scale, keep_first: int = 0, gate=None, split_weights: bool = False,
+                  sink=None, slopes=None, values_are_keys: bool = False):
         """Attention of the step's queries over the paged cache (kernel choice lives here)."""
         from . import attention_dispatch
-        return attention_dispatch.paged_attention(self, q, cache, ctx, window, scale, keep_first, gate, split_weights)
+        return attention_dispatch.paged_attention(self, q, cache, ctx, window, scale, keep_first, gate, split_weights,
+                                                  sink=sink, slopes=slopes, values_are_keys=values_are_keys)
 
 
 @dataclass
@@ -169,6 +171,7 @@ class Model:
     def forward(self, ctx, views) -> Optional[torch.Tensor]:
         """Run the step's tokens; ``views[e]`` is the cache view of schedule entry e."""
         h = ops.embed_gather(ctx.token_ids, self.embedding, self.spec.embedding_scale)
+        ctx.shared = {}
         pending = (None, None)
         for e, entry in enumerate(self.spec.schedule):
             pending = self.blocks[entry.layer].forward(h, pending, ctx, views[e])

@@ -80,8 +80,9 @@ def embed_gather(tokens: torch.Tensor, table: torch.Tensor, scale: float = 1.0) 
 
 def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], delta_bias: Optional[torch.Tensor],
                 weight: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
-                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``h += delta (+ bias)`` in place (float32), returns ``rmsnorm(h) * weight`` in ``out_dtype``.
+                rows: Optional[torch.Tensor] = None, delta2: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``h += delta (+ bias) (+ delta2)`` in place (float32), returns ``rmsnorm(h) * weight`` in ``out_dtype``.
+    ``delta2``: a second sublayer's output (float32, beside a ``delta``), added in the same pass.
 
     With ``rows`` only those rows are summed and normed, and ``h`` is left as it was.  ``weight`` may
     be ``None`` (no scaling: the weight was folded into the matrix that consumes the result).
@@ -97,12 +98,15 @@ def add_rmsnorm(h: torch.Tensor, delta: Optional[torch.Tensor], delta_bias: Opti
     if delta_bias is not None:
         _cuda_contig(delta_bias, "delta_bias", torch.float32)
         _need(delta is not None and delta_bias.numel() == H, "delta_bias needs a delta of the same width")
+    if delta2 is not None:
+        _cuda_contig(delta2, "delta2", torch.float32)
+        _need(delta is not None and tuple(delta2.shape) == (N, H), "a second delta comes beside a first of the same shape")
     if rows is not None:
         _cuda_contig(rows, "rows", torch.int32)
     n_out = N if rows is None else rows.numel()
     out = torch.empty((n_out, H), dtype=out_dtype, device=h.device)
     _lib.check(_lib.library().gesso_add_rmsnorm(
-        _p(h), _p(delta), _dt(delta) if delta is not None else F32, _p(delta_bias), _p(weight),
+        _p(h), _p(delta), _dt(delta) if delta is not None else F32, _p(delta_bias), _p(delta2), _p(weight),
         float(eps), _p(out), _dt(out), _p(rows), n_out, H, _stream()), "add_rmsnorm")
     return out
 
@@ -141,6 +145,17 @@ class PostNormed:
         add_dyt(h, self.delta, self.bias, self.post, None, None)
 
 
+class SummedDeltas:
+    """Two sublayers' outputs that are added to the residual stream together: ``h += first (+ bias) + second``
+    (a layer whose mixer and feed-forward read the same norm's output).  ``second`` is float32.  A norm that
+    understands it adds both in the pass of its own norm (``add_rmsnorm(..., delta2=)``)."""
+
+    __slots__ = ("first", "second")
+
+    def __init__(self, first: torch.Tensor, second: torch.Tensor):
+        self.first, self.second = first, second
+
+
 def add_dyt(h: torch.Tensor, delta: Optional[torch.Tensor], delta_bias: Optional[torch.Tensor],
             post: Optional[DytParams], pre: Optional[DytParams], out_dtype: Optional[torch.dtype],
             rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
@@ -175,7 +190,8 @@ def add_dyt(h: torch.Tensor, delta: Optional[torch.Tensor], delta_bias: Optional
 
 # ---- routed feed-forward ---------------------------------------------------------------------
 MOE_SCORES = {"sigmoid": 0, "softmax": 1}
-MOE_ACTS = {"relu2": 0, "silu": 1, "gelu_tanh": 2}
+MOE_ACTS = {"relu2": 0, "silu": 1, "gelu_tanh": 2, "glu_clamped": 3}
+MOE_GATED_ACTS = ("glu_clamped",)      # these take an expert's gate and up rows together: W_up [E, 2F, K]
 
 
 def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], top: int, n_groups: int,
@@ -201,24 +217,33 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torc
 
 
 def moe_experts_pairs(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, idx: torch.Tensor, w: torch.Tensor,
-                      act: str = "relu2") -> torch.Tensor:
+                      act: str = "relu2", limit: float = 0.0, glu_packed: bool = False,
+                      add_to: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``y[t] = sum_k w[t,k] * W_down[idx[t,k]] act(W_up[idx[t,k]] x[t])`` by (token, expert) pair; float32 [N, H].
-    ``w_up`` [E, F, K], ``w_down`` [E, H, F]."""
+    ``w_up`` [E, F, K] (a gated ``act``: [E, 2F, K], gate and up rows in groups of 8 + 8 with ``glu_packed``, else
+    all gate rows first; ``limit`` is the gated unit's clamp), ``w_down`` [E, H, F].  ``add_to``: float32 [N, H] that
+    the sums are added to (and that is returned)."""
     _cuda_contig(x, "x")
     _cuda_contig(w_up, "w_up")
     _cuda_contig(w_down, "w_down")
     N, K = x.shape
     E, F, K2 = w_up.shape
+    if act in MOE_GATED_ACTS:
+        _need(F % 2 == 0, "a gated activation takes gate and up rows: an even number of rows per expert")
+        F //= 2
     _need(K2 == K and tuple(w_down.shape[::2]) == (E, F), "expert matrices do not fit the rows")
     Hout = w_down.shape[1]
     top = idx.shape[1]
     a = torch.empty((N * top, F), dtype=x.dtype, device=x.device)
-    y = torch.empty((N, Hout), dtype=torch.float32, device=x.device)
+    if add_to is not None:
+        _cuda_contig(add_to, "add_to", torch.float32)
+        _need(tuple(add_to.shape) == (N, Hout), "add_to must be [tokens, outputs]")
+    y = add_to if add_to is not None else torch.empty((N, Hout), dtype=torch.float32, device=x.device)
     lib = _lib.library()
     _lib.check(lib.gesso_moe_pair_up(_p(x), _dt(x), _p(w_up), _dt(w_up), _p(idx), _p(a), N, top, K, F, MOE_ACTS[act],
-                                     _stream()), "moe_pair_up")
+                                     float(limit), 1 if glu_packed else 0, _stream()), "moe_pair_up")
     _lib.check(lib.gesso_moe_pair_down(_p(a), _dt(a), _p(w_down), _dt(w_down), _p(idx), _p(w), _p(y), N, top, F, Hout,
-                                       _stream()), "moe_pair_down")
+                                       1 if add_to is not None else 0, _stream()), "moe_pair_down")
     return y
 
 
@@ -231,22 +256,27 @@ _lib.declare("gesso_moe_grouped_rows", [_lib.LL, _lib.I])
 _lib.declare("gesso_moe_grouped_takes", [_lib.I, _lib.I, _lib.I])
 _lib.declare("gesso_moe_group_rows", [_lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P, _lib.P])
 _lib.declare("gesso_moe_gather_rows", [_lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.I, _lib.P])
-_lib.declare("gesso_moe_combine", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.I, _lib.P])
+_lib.declare("gesso_moe_combine", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.P])
 _lib.declare("gesso_moe_gemm_tcgen05", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.P, _lib.LL, _lib.I, _lib.I, _lib.I, _lib.I,
-                                        _lib.I, _lib.P, _lib.P])
+                                        _lib.I, _lib.F, _lib.P, _lib.P])
 
 
-def moe_grouped_takes(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, top: int) -> bool:
+def moe_grouped_takes(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, top: int, act: str = "relu2",
+                      glu_packed: bool = False) -> bool:
     """Whether the grouped tensor-core path takes this step (see :func:`moe_experts_grouped`): bfloat16 rows and
-    matrices, more pairs than go pair by pair, sizes in multiples of 8."""
+    matrices, more pairs than go pair by pair, sizes in multiples of 8; a gated activation in the packed layout."""
     E, F, K = w_up.shape
+    if act in MOE_GATED_ACTS:
+        if not glu_packed or F % 16 != 0:
+            return False
+        F //= 2
     return (x.dtype == torch.bfloat16 and w_up.dtype == torch.bfloat16 and w_down.dtype == torch.bfloat16
             and x.shape[0] * top > MOE_PAIR_MAX_ROWS
             and bool(_lib.library().gesso_moe_grouped_takes(K, F, w_down.shape[1])))
 
 
 def moe_experts_grouped(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, idx: torch.Tensor, w: torch.Tensor,
-                        act: str = "relu2") -> torch.Tensor:
+                        act: str = "relu2", limit: float = 0.0, add_to: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The same sum as :func:`moe_experts_pairs` with the rows grouped by expert and both products on the
     tcgen05 tensor cores (``csrc/moe_grouped.cu``); float32 [N, H].  Nothing here waits for the device: how
     many row tiles the routing made stays in device memory."""
@@ -256,9 +286,14 @@ def moe_experts_grouped(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tenso
     _cuda_contig(idx, "expert ids", torch.int32)
     _cuda_contig(w, "expert weights", torch.float32)
     N, K = x.shape
-    E, F, K2 = w_up.shape
+    E, F_up, K2 = w_up.shape
+    gated = act in MOE_GATED_ACTS            # W_up [E, 2F, K] in packed groups of 8 gate + 8 up rows
+    F = F_up // 2 if gated else F_up
     Hout = w_down.shape[1]
     _need(K2 == K and tuple(w_down.shape) == (E, Hout, F), "expert matrices do not fit the rows")
+    if add_to is not None:
+        _cuda_contig(add_to, "add_to", torch.float32)
+        _need(tuple(add_to.shape) == (N, Hout), "add_to must be [tokens, outputs]")
     top = idx.shape[1]
     pairs = N * top
     lib = _lib.library()
@@ -270,16 +305,18 @@ def moe_experts_grouped(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tenso
     a = torch.empty((rows, K), dtype=torch.bfloat16, device=dev)
     h = torch.empty((rows, F), dtype=torch.bfloat16, device=dev)
     c = torch.empty((rows, Hout), dtype=torch.float32, device=dev)
-    y = torch.empty((N, Hout), dtype=torch.float32, device=dev)
+    y = add_to if add_to is not None else torch.empty((N, Hout), dtype=torch.float32, device=dev)
     status = tc_status_tensor(dev)
     _lib.check(lib.gesso_moe_group_rows(_p(idx), pairs, E, _p(pair_row), _p(tile_expert), _p(n_tiles), _stream()),
                "moe_group_rows")
     _lib.check(lib.gesso_moe_gather_rows(_p(x), _p(pair_row), _p(a), pairs, top, K, _stream()), "moe_gather_rows")
-    _lib.check(lib.gesso_moe_gemm_tcgen05(_p(a), _p(w_up), _p(h), _p(tile_expert), _p(n_tiles), rows, E, F, K, 0,
-                                          MOE_ACTS[act], _p(status), _stream()), "moe_gemm_tcgen05 (up)")
+    _lib.check(lib.gesso_moe_gemm_tcgen05(_p(a), _p(w_up), _p(h), _p(tile_expert), _p(n_tiles), rows, E, F_up, K,
+                                          2 if gated else 0, MOE_ACTS[act], float(limit), _p(status), _stream()),
+               "moe_gemm_tcgen05 (up)")
     _lib.check(lib.gesso_moe_gemm_tcgen05(_p(h), _p(w_down), _p(c), _p(tile_expert), _p(n_tiles), rows, E, Hout, F, 1,
-                                          0, _p(status), _stream()), "moe_gemm_tcgen05 (down)")
-    _lib.check(lib.gesso_moe_combine(_p(c), _p(pair_row), _p(w), _p(y), N, top, Hout, _stream()), "moe_combine")
+                                          0, 0.0, _p(status), _stream()), "moe_gemm_tcgen05 (down)")
+    _lib.check(lib.gesso_moe_combine(_p(c), _p(pair_row), _p(w), _p(y), N, top, Hout, 1 if add_to is not None else 0,
+                                     _stream()), "moe_combine")
     return y
 
 
@@ -420,21 +457,33 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_w: Optional[torch.Tensor], k_w: Opti
 def paged_attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                             block_table: torch.Tensor, positions: torch.Tensor,
                             seg_of_token: torch.Tensor, window: Optional[int], scale: float,
-                            keep_first: int = 0, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                            keep_first: int = 0, gate: Optional[torch.Tensor] = None,
+                            sink: Optional[torch.Tensor] = None, slopes: Optional[torch.Tensor] = None,
+                            values_are_keys: bool = False) -> torch.Tensor:
     """FP32-arithmetic attention over the pages.  ``keep_first``: with a window, the first positions of the
     sequence that stay visible.  ``gate``: a 2-D view ``[N, nh * value size]`` with unit column stride (columns of
-    the fused projection, say) whose sigmoid multiplies the result."""
+    the fused projection, say) whose sigmoid multiplies the result.  ``sink``: float32 [nh], one more term
+    ``exp(sink[h])`` in the softmax denominator (no key, no value, not scaled).  ``slopes``: float32 [nh],
+    ``slopes[h] * (i - j)`` is taken off the score of key j for the query at i.  ``values_are_keys``: the weighted
+    sum runs over the key rows (``v_pages`` is not read): the absorbed form of latent attention.  ``q`` may be
+    float32 over bfloat16 pages; the result has the type of ``q``."""
     _cuda_contig(q, "q")
     N, nh, hd = q.shape
     nkv, page_size = k_pages.shape[1], k_pages.shape[2]
-    vd = v_pages.shape[2]
-    _need(k_pages.dtype == q.dtype, "cache pages must have the dtype of q")
+    vd = hd if values_are_keys else v_pages.shape[2]
+    _need(k_pages.dtype == q.dtype or (q.dtype == torch.float32 and k_pages.dtype == torch.bfloat16),
+          "cache pages must have the dtype of q (or be bfloat16 under a float32 q)")
+    for name, t in (("sink", sink), ("slopes", slopes)):
+        if t is not None:
+            _cuda_contig(t, name, torch.float32)
+            _need(t.numel() == nh, f"one {name} value per query head")
     out = torch.empty((N, nh * vd), dtype=q.dtype, device=q.device)
-    gate_stride = _check_gate(gate, N, nh * vd, q.dtype)
+    gate_stride = _check_gate(gate, N, nh * vd, k_pages.dtype)
     _lib.check(_lib.library().gesso_paged_attention_generic(
-        _p(q), _p(k_pages), _p(v_pages), _dt(q), _p(block_table), block_table.shape[1], page_size,
+        _p(q), _p(k_pages), _p(v_pages), _dt(k_pages), _p(block_table), block_table.shape[1], page_size,
         _p(positions), _p(seg_of_token), _p(out), N, nh, nkv, hd, int(window or 0), float(scale),
-        vd, int(keep_first or 0), _p(gate), gate_stride, _stream()), "paged_attention_generic")
+        vd, int(keep_first or 0), _p(gate), gate_stride, _dt(q), _p(sink), _p(slopes), 1 if values_are_keys else 0,
+        _stream()), "paged_attention_generic")
     return out
 
 
@@ -447,7 +496,142 @@ def _check_gate(gate: Optional[torch.Tensor], n: int, width: int, dtype) -> int:
     return int(gate.stride(0))
 
 
+# ---- short convolution on a projection's rows, latent attention, linear attention -------------------------
+def causal_conv(u: torch.Tensor, n_channels: int, bias: Optional[torch.Tensor], taps: torch.Tensor, state: torch.Tensor,
+                seg_of_token: torch.Tensor, seg_start: torch.Tensor, slots: torch.Tensor, n_segs: int,
+                mix: Optional[tuple] = None) -> torch.Tensor:
+    """A causal convolution over time on the first ``n_channels`` columns of ``u`` [N, >= C] (``bias`` [C] float32
+    is added first): ``y[t] = sum_j taps[:, j] * u'[t - (L-1) + j]`` inside a request, places before a portion's
+    start from ``state`` [slots, L-1, C] (float32), which is then moved on.  ``mix`` = (first, column 0, columns,
+    lambda): ``y[:, c0:c0+n] = (1 - lambda) * y[:, c0:c0+n] + lambda * first`` (``first`` a 2-D view of the run type
+    with unit column stride).  Returns y [N, C] in the type of ``u``."""
+    _need(u.is_cuda and u.dim() == 2 and u.stride(1) == 1, "u must be rows on the device with unit column stride")
+    _cuda_contig(taps, "taps", torch.float32)
+    N, C = u.shape[0], int(n_channels)
+    L = taps.shape[1]
+    _need(tuple(taps.shape) == (C, L) and u.shape[1] >= C, "taps must be [channels, taps] for the leading columns of u")
+    _need(L == 1 or (state.dtype == torch.float32 and state.is_cuda and state.dim() == 3
+                     and tuple(state.shape[1:]) == (L - 1, C) and state.stride(2) == 1 and state.stride(1) == C),
+          "conv state must be [slots, L-1, C] float32 with dense rows")
+    if bias is not None:
+        _cuda_contig(bias, "bias", torch.float32)
+        _need(bias.numel() >= C, "one bias value per channel")
+    for name, t in (("seg_of_token", seg_of_token), ("seg_start", seg_start), ("slots", slots)):
+        _cuda_contig(t, name, torch.int32)
+    first, first_stride, c0, n_mix, lam = None, 0, 0, 0, 0.0
+    if mix is not None:
+        first, c0, n_mix, lam = mix
+        _need(first.is_cuda and first.dim() == 2 and tuple(first.shape) == (N, n_mix) and first.stride(1) == 1
+              and first.dtype == u.dtype, "the values to mix in must be [tokens, columns] of the run type")
+        first_stride = int(first.stride(0))
+    out = torch.empty((N, C), dtype=u.dtype, device=u.device)
+    _lib.check(_lib.library().gesso_causal_conv(
+        _p(u), _dt(u), int(u.stride(0)), _p(bias), _p(taps), _p(state), state.stride(0), _p(seg_of_token), _p(seg_start),
+        _p(slots), _p(out), N, int(n_segs), C, L, _p(first), first_stride, int(c0), int(n_mix), float(lam), _stream()),
+        "causal_conv")
+    return out
+
+
+def latent_norm_store(proj: torch.Tensor, q_rank: int, kv_rank: int, wq: Optional[torch.Tensor],
+                      wkv: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype, positions: torch.Tensor,
+                      seg_of_token: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor, write_kv: bool,
+                      status: torch.Tensor) -> Optional[torch.Tensor]:
+    """RMS-norm the two latents of the fused down projection ``proj`` (float32 [N, q_rank + kv_rank]) with their
+    weights; returns the query latent [N, q_rank] in ``out_dtype`` and writes the key/value latent into the
+    position's slot of ``k_pages`` ([pages, 1, page size, kv_rank])."""
+    _cuda_contig(proj, "proj", torch.float32)
+    N = proj.shape[0]
+    _need(proj.shape[1] == q_rank + kv_rank, "the fused projection must hold the two latents side by side")
+    for t, n in ((wq, q_rank), (wkv, kv_rank)):
+        if n:
+            _cuda_contig(t, "latent norm weight", torch.float32)
+            _need(t.numel() == n, "one norm weight per latent feature")
+    _need(k_pages.is_contiguous() and k_pages.dtype == out_dtype and k_pages.dim() == 4 and k_pages.shape[1] == 1
+          and (not write_kv or k_pages.shape[3] == kv_rank),
+          "latent pages must be [pages, 1, page size, kv_rank] of the run dtype")
+    cq = torch.empty((N, q_rank), dtype=out_dtype, device=proj.device) if q_rank else None
+    _lib.check(_lib.library().gesso_latent_norm_store(
+        _p(proj), int(q_rank), int(kv_rank), _p(wq), _p(wkv), float(eps), _p(cq), _dt(k_pages), _p(positions),
+        _p(seg_of_token), _p(block_table), block_table.shape[1], k_pages.shape[2], _p(k_pages), 1 if write_kv else 0,
+        _p(status), N, _stream()), "latent_norm_store")
+    return cq
+
+
+def headwise_linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """``out[n, h, o] = sum_i w[h, i, o] * x[n, h, i]`` for per-head matrices ``w`` [H, I, O] (input-major); ``x``
+    [N, H, I]; float32 accumulation; returns [N, H, O] in ``out_dtype``."""
+    _cuda_contig(x, "x")
+    _cuda_contig(w, "w")
+    N, H, I = x.shape
+    _need(w.dim() == 3 and w.shape[0] == H and w.shape[1] == I, "per-head matrices must be [heads, inputs, outputs]")
+    O = w.shape[2]
+    out = torch.empty((N, H, O), dtype=out_dtype, device=x.device)
+    _lib.check(_lib.library().gesso_headwise_linear(_p(x), _dt(x), _p(w), _dt(w), _p(out), _dt(out), N, H, I, O,
+                                                    _stream()), "headwise_linear")
+    return out
+
+
+def lightning_attention(proj: torch.Tensor, state: torch.Tensor, decay: torch.Tensor, seg_start: torch.Tensor,
+                        slots: torch.Tensor, n_segs: int, n_heads: int, dim: int, vdim: int) -> torch.Tensor:
+    """Linear attention with a per-head decay as a recurrence: ``S = decay * S + k v^T``, ``o = S^T q`` with q, k, v
+    = silu of the columns of ``proj`` [N, >= 2*H*D + H*Dv] (q, then k, then v, head by head).  ``state``: [slots, H,
+    Dv, D] float32, read at a segment's start and left as its last token makes it.  Returns o [N, H * Dv] float32."""
+    _need(proj.is_cuda and proj.dim() == 2 and proj.stride(1) == 1, "proj must be rows on the device")
+    H, D, Dv = int(n_heads), int(dim), int(vdim)
+    _need(proj.shape[1] >= 2 * H * D + H * Dv, "proj is narrower than q, k and v")
+    _need(state.dtype == torch.float32 and state.is_cuda and tuple(state.shape[1:]) == (H, Dv, D)
+          and state[0].is_contiguous(), "state must be [slots, heads, value size, key size] float32")
+    _cuda_contig(decay, "decay", torch.float32)
+    _need(decay.numel() == H, "one decay per head")
+    _cuda_contig(seg_start, "seg_start", torch.int32)
+    _cuda_contig(slots, "slots", torch.int32)
+    N = proj.shape[0]
+    out = torch.empty((N, H * Dv), dtype=torch.float32, device=proj.device)
+    _lib.check(_lib.library().gesso_lightning(_p(proj), _dt(proj), int(proj.stride(0)), _p(state), state.stride(0),
+                                              _p(decay), _p(seg_start), _p(slots), _p(out), N, int(n_segs), H, D, Dv,
+                                              _stream()), "lightning")
+    return out
+
+
+def gated_rmsnorm(o: torch.Tensor, weight: torch.Tensor, eps: float, gate: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """``rmsnorm(o) * weight * sigmoid(gate)`` over rows of float32 ``o`` [N, W]; ``gate`` a 2-D view [N, W] of
+    ``out_dtype`` with unit column stride."""
+    _cuda_contig(o, "o", torch.float32)
+    _cuda_contig(weight, "weight", torch.float32)
+    N, W = o.shape
+    _need(weight.numel() == W, "one norm weight per column")
+    _need(gate.is_cuda and tuple(gate.shape) == (N, W) and gate.stride(1) == 1 and gate.dtype == out_dtype,
+          "gate must be [rows, columns] of the output type with unit column stride")
+    out = torch.empty((N, W), dtype=out_dtype, device=o.device)
+    _lib.check(_lib.library().gesso_gated_rmsnorm(_p(o), _p(weight), float(eps), _p(gate), int(gate.stride(0)), _p(out),
+                                                  _dt(out), N, W, _stream()), "gated_rmsnorm")
+    return out
+
+
 # ---- feed-forward ------------------------------------------------------------------------------
+def gelu_erf(x: torch.Tensor) -> torch.Tensor:
+    """The exact gelu, ``0.5 x (1 + erf(x / sqrt 2))``, evaluated in float32."""
+    _cuda_contig(x, "x")
+    out = torch.empty_like(x)
+    _lib.check(_lib.library().gesso_gelu_erf(_p(x), _p(out), _dt(x), x.numel(), _stream()), "gelu_erf")
+    return out
+
+
+GLU_ALPHA = 1.702
+
+
+def glu_clamped(gu: torch.Tensor, limit: float, packed: bool = False) -> torch.Tensor:
+    """``g * sigmoid(1.702 g) * (u + 1)`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)`` on the fused
+    projection [N, 2F] (plain: gate columns, then up columns; ``packed``: groups of 8 gate + 8 up columns)."""
+    _cuda_contig(gu, "gate_up")
+    N, F2 = gu.shape
+    _need(F2 % 2 == 0 and (not packed or F2 % 16 == 0), "fused gate/up width does not fit the layout")
+    out = torch.empty((N, F2 // 2), dtype=gu.dtype, device=gu.device)
+    _lib.check(_lib.library().gesso_glu_clamped(_p(gu), _p(out), _dt(gu), N, F2 // 2, 1 if packed else 0, float(limit),
+                                                GLU_ALPHA, _stream()), "glu_clamped")
+    return out
+
+
 def swiglu(gu: torch.Tensor, packed: bool = False) -> torch.Tensor:
     """``silu(gate) * up`` on the fused projection [N, 2F].  Plain layout: gate columns first, then
     up columns.  ``packed``: groups of 16 columns hold 8 gate and then the matching 8 up columns."""

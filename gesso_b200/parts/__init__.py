@@ -3,7 +3,8 @@ from .base import (FeedForward, Mixer, Norm, PagedNeed, ParamDecl, Part, Positio
 from .registry import (build_block, build_feed_forward, build_mixer, build_norm, build_position,
                        register_block, register_feed_forward, register_mixer, register_norm,
                        register_position, registered, unregister)
-from . import attention, block, feed_forward, norm, rope, routed_experts, short_conv  # noqa: F401  (register the built-in parts)
+from . import (attention, block, feed_forward, latent_attention, lightning, norm, rope, routed_experts,  # noqa: F401
+               short_conv)  # noqa: F401  (register the built-in parts)
 
 __all__ = [
     "FeedForward", "Mixer", "Norm", "PagedNeed", "ParamDecl", "Part", "Position", "StateNeed",

@@ -11,6 +11,8 @@ added at once: it travels as ``pending = (delta, bias)`` to the next norm, which
 path, src/Inference/Inference.jl:3239-3247).
 
 ``sandwich``: each sublayer's output is normed once more before it is added (see :class:`SandwichBlock`).
+
+``parallel``: one norm, whose output both sublayers read (see :class:`ParallelBlock`).
 """
 from __future__ import annotations
 
@@ -138,5 +140,51 @@ class SandwichBlock:
         return ops.PostNormed(d, self.ff_post_norm.params(), b), None
 
 
+class ParallelBlock:
+    """One norm per layer, and both sublayers read its output::
+
+        n = Norm(h);   h = h + (Mixer(n) + FeedForward(n))        (the feed-forward may be left out)
+
+    The two outputs travel on together (``ops.SummedDeltas``): the next layer's norm adds both into the float32
+    stream in the pass of its own norm.  The feed-forward's output is float32; the mixer's may be of the run type."""
+
+    def __init__(self, block_spec):
+        self.spec = block_spec
+        self.mixer = build_mixer(block_spec.mixer)
+        self.mixer_norm = build_norm(block_spec.mixer_norm)
+        self.feed_forward = None if block_spec.feed_forward is None else build_feed_forward(block_spec.feed_forward)
+
+    def parts(self):
+        out = [("mixer_norm.", self.mixer_norm), ("mixer.", self.mixer)]
+        if self.feed_forward is not None:
+            out.append(("feed_forward.", self.feed_forward))
+        return tuple(out)
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        out = {}
+        for prefix, part in self.parts():
+            for name, decl in part.param_decls().items():
+                out[prefix + name] = decl
+        return out
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def bind(self, tensors, rt) -> None:
+        for prefix, part in self.parts():
+            part.bind({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)}, rt)
+
+    def forward(self, h, pending, ctx, cache):
+        x = self.mixer_norm.add_norm(h, pending[0], pending[1])
+        d, b = self.mixer.forward(x, ctx, cache)
+        if self.feed_forward is None:
+            return d, b
+        f, fb = self.feed_forward.forward(x, ctx)
+        if fb is not None:
+            raise invalid("parallel block: a feed-forward with an output bias is not supported")
+        return ops.SummedDeltas(d, f), b
+
+
+register_block("parallel", ParallelBlock, replace=True)
 register_block("prenorm", PreNormBlock, replace=True)
 register_block("sandwich", SandwichBlock, replace=True)

@@ -1,8 +1,17 @@
-"""SwiGLU feed-forward: ``down( silu(gate(x)) * up(x) )``, no biases.
+"""Dense feed-forwards.
+
+``swiglu``: ``down( silu(gate(x)) * up(x) )``, no biases.
 
 ``g = x Wg^T``, ``u = x Wu^T``, ``a = (g / (1 + exp(-g))) * u``, ``d = a Wd^T``
 (src/Inference/Inference.jl:869-882, src/Operators/cpu.jl:482-488).  Gate and up are fused
 into one matrix at bind time.
+
+``mlp``: ``down( act(up(x)) )`` with one activation between two matrices, no biases; ``activation`` is a parameter
+(``gelu_erf``: the exact gelu, ``0.5 z (1 + erf(z / sqrt 2))``).  Its output is float32.
+
+``glu_clamped``: a gated unit with clamped inputs, ``down( g * sigmoid(1.702 g) * (u + 1) )`` with ``g = min(gate(x),
+limit)`` and ``u = clamp(up(x), -limit, limit)``; ``limit`` is a parameter.  Its output is float32.  (The routed
+feed-forward uses the same unit for its experts and runs one of these as its shared expert.)
 """
 from __future__ import annotations
 
@@ -11,6 +20,7 @@ from typing import Dict
 import torch
 
 from .. import ops
+from ..errors import invalid
 from .base import FeedForward, ParamDecl
 from .registry import register_feed_forward
 
@@ -54,4 +64,52 @@ class SwiGLU(FeedForward):
         return ops.linear(a, self.w_down, out_dtype=a.dtype), None
 
 
+class MLP(FeedForward):
+    ACTIVATIONS = {"gelu_erf": ops.gelu_erf}
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden = int(spec["hidden_size"])
+        self.ff = int(spec["ff_dim"])
+        self.act = str(spec.get("activation", "gelu_erf"))
+        if self.act not in self.ACTIVATIONS:
+            raise invalid(f"mlp: unknown activation {self.act!r}; known: {sorted(self.ACTIVATIONS)}")
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        return {"up.weight": ParamDecl((self.ff, self.hidden), fan_in=self.hidden),
+                "down.weight": ParamDecl((self.hidden, self.ff), fan_in=self.ff)}
+
+    def bind(self, tensors, rt) -> None:
+        self.w_up, self.w_down = tensors["up.weight"], tensors["down.weight"]
+
+    def forward(self, x, ctx):
+        a = self.ACTIVATIONS[self.act](ops.linear(x, self.w_up, out_dtype=x.dtype))
+        return ops.linear(a, self.w_down, out_dtype=torch.float32), None
+
+
+class ClampedGLU(FeedForward):
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden = int(spec["hidden_size"])
+        self.ff = int(spec["ff_dim"])
+        self.limit = float(spec["limit"])
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        return {"gate.weight": ParamDecl((self.ff, self.hidden), fan_in=self.hidden),
+                "up.weight": ParamDecl((self.ff, self.hidden), fan_in=self.hidden),
+                "down.weight": ParamDecl((self.hidden, self.ff), fan_in=self.ff)}
+
+    def bind(self, tensors, rt) -> None:
+        g, u = tensors["gate.weight"], tensors["up.weight"]
+        common = torch.float32 if (g.dtype == torch.float32 or u.dtype == torch.float32) else g.dtype
+        self.w_gate_up = torch.cat([g.to(common), u.to(common)], dim=0).contiguous()
+        self.w_down = tensors["down.weight"]
+
+    def forward(self, x, ctx):
+        a = ops.glu_clamped(ops.linear(x, self.w_gate_up, out_dtype=x.dtype), self.limit)
+        return ops.linear(a, self.w_down, out_dtype=torch.float32), None
+
+
 register_feed_forward("swiglu", SwiGLU, replace=True)
+register_feed_forward("mlp", MLP, replace=True)
+register_feed_forward("glu_clamped", ClampedGLU, replace=True)

@@ -1,0 +1,108 @@
+"""Latent attention: queries, keys and values that go through low-rank latents; only the key/value latent is cached.
+
+With the mixer's input ``x`` (own notation; ``N(.; w)`` is an RMS norm with a plain weight)::
+
+    c_q = N(W_dq x; w_q)          q_h = W_uq[h] c_q                       (H heads of ``head_dim``)
+    c   = N(W_dkv x; w_kv)        k_h = W_uk[h] c,   v_h = W_uv[h] c      (``kv_rank`` numbers per position)
+    score_h(i, j) = scale * q_h(i) . k_h(j)   for 0 <= i - j < window
+    p = softmax over the visible keys, with one more term exp(sink_h) in the denominator (``sink``)
+    out = W_o concat_h( sum_j p_h(i, j) v_h(j) )
+
+There are no positions in it.  The cache holds ``c`` alone: one "kv head" of ``kv_rank`` features per position and
+no value pages.  The engine evaluates the *absorbed* form, which reads the cached latent directly::
+
+    q'_h = W_uk[h]^T q_h                    (carried into the latent space: kv_rank features, float32)
+    a_h  = sum_j p_h(i, j) c(j)             (scores q'_h . c(j); keys and values are the same rows)
+    o_h  = W_uv[h] a_h
+
+so that a step never expands keys and values of cached positions, whether it decodes or reads a prompt.
+
+Parameters: hidden_size, n_heads, head_dim, v_head_dim, q_rank, kv_rank, scale, window (``None``: all keys), sink
+(default true), norm_eps.  Tensors: ``dq.weight`` [q_rank, hidden], ``dq_norm.weight`` [q_rank], ``uq.weight`` [H *
+head_dim, q_rank], ``dkv.weight`` [kv_rank, hidden], ``dkv_norm.weight`` [kv_rank], ``uk.weight`` [H * head_dim,
+kv_rank], ``uv.weight`` [H * v_head_dim, kv_rank], ``sink`` [H], ``o_proj.weight`` [hidden, H * v_head_dim].
+
+What is 32-bit whatever the run type: both latent norms (on the float32 sums of the down projection), q', the
+scores, the softmax with its sink, and the weighted sum of latents.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from .. import ops
+from ..errors import invalid
+from .base import Mixer, PagedNeed, ParamDecl
+from .registry import register_mixer
+
+
+class LatentAttention(Mixer):
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.hidden = int(spec["hidden_size"])
+        self.nh = int(spec["n_heads"])
+        self.hd = int(spec["head_dim"])
+        self.vd = int(spec.get("v_head_dim") or self.hd)
+        self.q_rank = int(spec["q_rank"])
+        self.kv_rank = int(spec["kv_rank"])
+        self.scale = float(spec["scale"]) if spec.get("scale") is not None else float(self.hd) ** -0.5
+        self.window = spec.get("window")
+        self.has_sink = bool(spec.get("sink", True))
+        self.eps = float(spec["norm_eps"])
+        if min(self.nh, self.hd, self.vd, self.q_rank, self.kv_rank) < 1:
+            raise invalid("latent attention: sizes must be positive")
+        if self.kv_rank > 256:
+            raise invalid(f"latent attention: kv_rank {self.kv_rank} is above 256, the most the attention kernel takes")
+        if self.window is not None and int(self.window) < 1:
+            raise invalid("latent attention: window must be >= 1")
+
+    def param_decls(self) -> Dict[str, ParamDecl]:
+        H, D, Dv, Rq, R, W = self.nh, self.hd, self.vd, self.q_rank, self.kv_rank, self.hidden
+        d = {
+            "dq.weight": ParamDecl((Rq, W), fan_in=W),
+            "dq_norm.weight": ParamDecl((Rq,), role="vector", init="ones"),
+            "uq.weight": ParamDecl((H * D, Rq), fan_in=Rq),
+            "dkv.weight": ParamDecl((R, W), fan_in=W),
+            "dkv_norm.weight": ParamDecl((R,), role="vector", init="ones"),
+            "uk.weight": ParamDecl((H * D, R), fan_in=R),
+            "uv.weight": ParamDecl((H * Dv, R), fan_in=R),
+            "o_proj.weight": ParamDecl((W, H * Dv), fan_in=H * Dv),
+        }
+        if self.has_sink:
+            d["sink"] = ParamDecl((H,), role="vector", init="zeros")
+        return d
+
+    def cache_need(self):
+        # one latent per position: a single kv head of kv_rank features, and no value pages
+        return PagedNeed(1, self.kv_rank, int(self.window) if self.window is not None else None, 0, 0)
+
+    def bind(self, tensors, rt) -> None:
+        H, D, Dv, R = self.nh, self.hd, self.vd, self.kv_rank
+        ws = [tensors["dq.weight"], tensors["dkv.weight"]]
+        common = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
+        self.w_down = torch.cat([w.to(common) for w in ws], dim=0).contiguous()          # [Rq + R, hidden]
+        self.w_dq = ws[0].contiguous()
+        self.wn_q, self.wn_kv = tensors["dq_norm.weight"], tensors["dkv_norm.weight"]
+        self.w_uq = tensors["uq.weight"]
+        # per head, input-major: q' = W_uk[h]^T q ([D, R] as stored), o = W_uv[h] a ([R, Dv]: transposed once)
+        self.w_absorb = tensors["uk.weight"].reshape(H, D, R).contiguous()
+        self.w_expand = tensors["uv.weight"].reshape(H, Dv, R).transpose(1, 2).contiguous()
+        self.sink = tensors["sink"].float().contiguous() if self.has_sink else None
+        self.w_o = tensors["o_proj.weight"]
+        self.rt = rt
+
+    def forward(self, x, ctx, cache):
+        writes = cache.writes
+        Rq, R = self.q_rank, self.kv_rank
+        proj = ops.linear(x, self.w_down if writes else self.w_dq, out_dtype=torch.float32)
+        cq = ops.latent_norm_store(proj, Rq, R if writes else 0, self.wn_q, self.wn_kv, self.eps, x.dtype,
+                                   ctx.positions, ctx.seg_of_token, cache.block_table, cache.k_pages, writes, ctx.status)
+        q = ops.linear(cq, self.w_uq, out_dtype=x.dtype).view(-1, self.nh, self.hd)
+        q_lat = ops.headwise_linear(q, self.w_absorb, torch.float32)                      # [N, H, R]
+        a = self.rt.attention(q_lat, cache, ctx, self.window, self.scale, sink=self.sink, values_are_keys=True)
+        o = ops.headwise_linear(a.view(-1, self.nh, R), self.w_expand, x.dtype)           # [N, H, Dv]
+        return ops.linear(o.view(-1, self.nh * self.vd), self.w_o, out_dtype=torch.float32), None
+
+
+register_mixer("latent_attention", LatentAttention, replace=True)

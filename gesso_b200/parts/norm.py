@@ -4,6 +4,10 @@
 second (src/Operators/cpu.jl:293-311).  The residual stream is float32; the sum
 and the statistics are float32, the output is rounded to the run dtype.
 
+With the parameter ``unit_offset`` the weight tensor holds the scale's offset from one, ``scale = 1 + w`` (formed once, in
+float32, when the weights are bound).  A pending :class:`~gesso_b200.ops.SummedDeltas` (two sublayers' outputs
+that are added together) is added in the same pass.
+
 With ``lazy=True`` and nothing to add, the norm is not run: a
 :class:`~gesso_b200.ops.LazyNorm` is returned, which the consumer's first matrix
 product applies in its prologue for steps of few tokens (or materialises).
@@ -26,15 +30,18 @@ class RMSNorm(Norm):
         super().__init__(spec)
         self.size = int(spec["size"])
         self.eps = float(spec["eps"])
+        self.unit_offset = bool(spec.get("unit_offset", False))
         self.weight = None
         self.out_dtype = None
         self.folded = False      # True once the consumer's matrix carries this norm's weight
 
     def param_decls(self) -> Dict[str, ParamDecl]:
-        return {"weight": ParamDecl((self.size,), role="vector", init="ones")}
+        return {"weight": ParamDecl((self.size,), role="vector", init="zeros" if self.unit_offset else "ones")}
 
     def bind(self, tensors, rt) -> None:
         self.weight = tensors["weight"]
+        if self.unit_offset:
+            self.weight = (self.weight.float() + 1.0).contiguous()
         self.out_dtype = rt.dtype
 
     def fold_into(self, consumer) -> bool:
@@ -53,10 +60,13 @@ class RMSNorm(Norm):
                 raise NotImplementedError("rmsnorm: a post-normed delta cannot be added for a row list")
             delta.add_into(h)
             delta = None
+        delta2 = None
+        if isinstance(delta, ops.SummedDeltas):    # two sublayers' outputs, added in this pass
+            delta, delta2 = delta.first, delta.second
         weight = None if self.folded else self.weight
         if lazy and delta is None and rows is None:
             return ops.LazyNorm(h, weight, self.eps, self.out_dtype)
-        return ops.add_rmsnorm(h, delta, delta_bias, weight, self.eps, self.out_dtype, rows)
+        return ops.add_rmsnorm(h, delta, delta_bias, weight, self.eps, self.out_dtype, rows, delta2=delta2)
 
 
 class DynamicTanh(Norm):
