@@ -44,6 +44,11 @@ a step;
                                              # Tanh norms) at three sizes beside all-attention LFM2 layers of equal
                                              # size: prefill and decode throughput, and both models' kernels by name
 
+    python bench.py --workload memipel       # Memipel layers (latent attention with a sink, convolved attention with
+                                             # a distance bias, lightning attention; dense, routed and shared gated
+                                             # feed-forwards in parallel with the mixer) at two sizes beside Sodurax
+                                             # layers of equal size: prefill and decode throughput, kernels by name
+
 a table (not JSON) of where a step's time goes, from the CUPTI activity trace.
 
 Peaks come from ``MEASURED_PEAKS.json`` beside this file when the driver wrote it, else the
@@ -594,6 +599,134 @@ def sodurax_workload(args) -> int:
         "peaks": pk, "sizes": out, "clocks": sampler.summary()}))
     return 0
 
+# ---- Memipel beside Sodurax at equal size -----------------------------------------------------------------------
+# Six layers in the order lightning, latent attention, attention, twice; the first layer's feed-forward is dense,
+# the others are routed with a shared expert.  The Sodurax model beside it has six attention layers of the same
+# width, heads, window and experts (its closest relative: windowed attention with biased projections and routed
+# experts chosen by groups).
+MEMIPEL_SIZES = {
+    "w1024": dict(width=1024, heads=16, kv=4, dim=64, q_rank=384, kv_rank=128, lt_heads=16, lt_dim=64, experts=16, ff=512,
+                  top=4, groups=4, keep=2, window=1024, conv=3),
+    "w2048": dict(width=2048, heads=32, kv=8, dim=64, q_rank=768, kv_rank=256, lt_heads=16, lt_dim=128, experts=32,
+                  ff=1024, top=4, groups=8, keep=4, window=2048, conv=4),
+}
+MEMIPEL_LAYERS = 6
+
+
+def memipel_configs(z):
+    moe = {"kind": "moe", "expert": {"ff": z["ff"], "limit": 7.0},
+           "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": z["groups"], "keep": z["keep"]}},
+           "shared": {"ff": z["ff"], "limit": 7.0}}
+    H = z["lt_heads"]
+    lightning = {"type": "lightning", "mixer": {"heads": H, "dim": z["lt_dim"], "vdim": z["lt_dim"],
+                                                "decay": [1.0 - 2.0 ** -(1 + 8 * h / H) for h in range(H)]}, "mlp": moe}
+    latent = {"type": "latent_attention",
+              "mixer": {"heads": z["heads"], "dim": z["dim"], "vdim": z["dim"], "q_rank": z["q_rank"], "kv_rank": z["kv_rank"],
+                        "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]}}, "mlp": moe}
+    attention = {"type": "attention",
+                 "mixer": {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+                           "conv": z["conv"], "v_mix": True, "mask": {"size": z["window"]}}, "mlp": moe}
+    layers = [dict(lightning, mlp={"kind": "dense", "ff": z["top"] * z["ff"]}), latent, attention, lightning, latent, attention]
+    mmp = {"architecture": "Memipel", "vocab": SODURAX_VOCAB, "width": z["width"], "norm": {"eps": 1e-6}, "layers": layers}
+    sdx, _ = sodurax_configs(dict(z, first=4, rot=32))
+    sdx["layers"] = [sdx["layers"][0] for _ in range(MEMIPEL_LAYERS)]
+    return mmp, sdx
+
+
+def memipel_workload(args) -> int:
+    import torch
+    import gesso_b200 as gb
+    from gesso_b200.engine.batch import StepEntry
+    from gesso_b200.engine.engine import Engine
+    from gesso_b200 import ops
+    pk = peaks()
+    warmup = max(args.warmup, 3)
+    steps = min(args.steps, 64)
+    sampler = ClockSampler(device_uuid())
+    sampler.start()
+    out = {}
+    for name, z in MEMIPEL_SIZES.items():
+        if args.sizes and name not in args.sizes.split(","):
+            continue
+        row = {}
+        for which, cfg in zip(("memipel", "sodurax"), memipel_configs(z)):
+            model = gb.random_model(cfg, seed=0, dtype="bfloat16", max_positions=args.context, style="fan_in")
+            ms_pre = time_prefill(gb, model, args.prefill_tokens, args.page_size)
+            ms_dec, launches, kv_mid = time_decode(gb, model, args.batch, args.context, steps, warmup, args.page_size)
+            # Bytes of a decoding step: the matrices it reads once (routed experts: those that batch * top pairs touch)
+            # and what a query reads of the cache (latents, keys and values inside the window; a lightning state is
+            # read and written).  Flops of a prefill step: the matrices a token uses and the windowed causal attention
+            # (latent attention in the absorbed form: kv_rank features for scores and for values, per head).
+            W, H, G, D, T = z["width"], z["heads"], z["kv"], z["dim"], args.prefill_tokens
+            touched = min(z["experts"], args.batch * z["top"])
+            keys, keys_pre = min(kv_mid, z["window"]), min(T / 2, z["window"])
+            if which == "memipel":
+                LH, LD, Rq, R = z["lt_heads"], z["lt_dim"], z["q_rank"], z["kv_rank"]
+                moe_dec = touched * 3 * z["ff"] * W + z["experts"] * W + 3 * z["ff"] * W
+                moe_tok = (z["top"] + 1) * 3 * z["ff"] * W + z["experts"] * W
+                mix_w = {"lightning": 4 * LH * LD * W + LH * LD * W,
+                         "latent": (Rq + R) * W + H * D * Rq + 2 * H * D * R + H * D * W,
+                         "attention": W * (H * D + 2 * G * D) + H * D * W}
+                cache_dec = {"lightning": 2 * LH * LD * LD * 4, "latent": keys * R * 2, "attention": keys * 2 * G * D * 2}
+                attn_pre = {"lightning": 2 * LH * LD * LD, "latent": 2 * keys_pre * H * R, "attention": 2 * keys_pre * H * D}
+                order = ["lightning", "latent", "attention"] * 2
+                ffs_dec = [2 * z["top"] * z["ff"] * W] + [moe_dec] * 5
+                ffs_tok = [2 * z["top"] * z["ff"] * W] + [moe_tok] * 5
+                w_dec = sum(mix_w[k] for k in order) + sum(ffs_dec)
+                w_tok = sum(mix_w[k] for k in order) + sum(ffs_tok)
+                cache = sum(cache_dec[k] for k in order)
+                attn = sum(attn_pre[k] for k in order)
+            else:
+                attn_w = W * (H * D + 2 * G * D) + 2 * H * D * W
+                w_dec = MEMIPEL_LAYERS * (attn_w + touched * 2 * z["ff"] * W + z["experts"] * W)
+                w_tok = MEMIPEL_LAYERS * (attn_w + z["top"] * 2 * z["ff"] * W + z["experts"] * W)
+                cache = MEMIPEL_LAYERS * min(kv_mid, z["window"] + 4) * 2 * G * D * 2
+                attn = MEMIPEL_LAYERS * 2 * keys_pre * H * D
+            head = SODURAX_VOCAB * W
+            dec_bytes = 2 * (w_dec + head) + args.batch * cache
+            pre_flops = T * 2 * (w_tok + attn)
+            row[which] = {
+                "prefill_ms": round(ms_pre, 4), "prefill_tok_s": round(T * 1000 / ms_pre, 1),
+                "prefill_frac_of_bf16_peak": round(pre_flops / (ms_pre * 1e-3) / 1e12 / pk["bf16_tflops"], 4),
+                "decode_ms_per_step": round(ms_dec, 4), "decode_tok_s": round(args.batch * 1000 / ms_dec, 1),
+                "decode_frac_of_hbm_peak": round(dec_bytes / (ms_dec * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
+                "gpu_launches_per_decode_step": launches // steps}
+            if args.kernels:
+                eng = Engine(model, max_positions=args.context, page_size=args.page_size,
+                             num_pages=(args.batch + 1) * (args.context // args.page_size + 1), max_requests=args.batch + 1)
+                g = torch.Generator().manual_seed(5)
+                prompt = torch.randint(0, model.vocab_size, (T,), generator=g).tolist()
+                for i in range(args.batch):
+                    eng.admit(i)
+                    eng.step([StepEntry(i, prompt, [])])
+                n_pre = [0]
+
+                def pre():
+                    rid = f"p{n_pre[0]}"
+                    n_pre[0] += 1
+                    eng.admit(rid)
+                    eng.step([StepEntry(rid, prompt, [T - 1])])
+                    eng.release(rid)
+
+                def dec():
+                    ops.argmax_rows(eng.step([StepEntry(i, [7 + i], [0]) for i in range(args.batch)]))
+                for _ in range(3):                  # the steps' graphs are captured
+                    pre(), dec()
+                row[which]["prefill_kernels_us"] = kernels_by_name(pre)
+                row[which]["decode_kernels_us"] = kernels_by_name(dec)
+                eng.check_status()
+            del model
+            torch.cuda.empty_cache()
+        row["prefill_ratio"] = round(row["memipel"]["prefill_tok_s"] / row["sodurax"]["prefill_tok_s"], 3)
+        row["decode_ratio"] = round(row["memipel"]["decode_tok_s"] / row["sodurax"]["decode_tok_s"], 3)
+        out[name] = dict(row, sizes=z)
+    print(json.dumps({
+        "workload": "memipel", "metric": "prefill and decode tokens/s of Memipel layers beside Sodurax layers of equal size",
+        "unit": "tokens/s", "layers": MEMIPEL_LAYERS, "vocab": SODURAX_VOCAB, "batch": args.batch, "context": args.context,
+        "prefill_tokens": args.prefill_tokens, "dtype": "bf16", "data": "synthetic (uniform-random token ids, random weights seed 0)",
+        "peaks": pk, "sizes": out, "clocks": sampler.summary()}))
+    return 0
+
 
 def reference_arm():
     """The reference is a Julia 1.12 project (Project.toml, no setup.py / pyproject.toml): pip cannot
@@ -617,12 +750,12 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
-    ap.add_argument("--workload", default="decode", choices=["decode", "timeline", "sodurax"] + sorted(SERVE),
+    ap.add_argument("--workload", default="decode", choices=["decode", "timeline", "sodurax", "memipel"] + sorted(SERVE),
                     help="decode: the headline (default); serve350m / serve700m: serving-like runs through run_batch; "
                          "timeline: the kernels of one decoding step at --batch and --context; sodurax: Sodurax layers "
-                         "beside LFM2 attention layers of equal size")
-    ap.add_argument("--sizes", default="", help="sodurax workload: which of its sizes to run, with commas (default: all)")
-    ap.add_argument("--kernels", action="store_true", help="sodurax workload: also the kernels of a step by name")
+                         "beside LFM2 attention layers of equal size; memipel: Memipel layers beside Sodurax layers of equal size")
+    ap.add_argument("--sizes", default="", help="sodurax / memipel workload: which of its sizes to run, with commas (default: all)")
+    ap.add_argument("--kernels", action="store_true", help="sodurax / memipel workload: also the kernels of a step by name")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -633,6 +766,8 @@ def main() -> int:
         return kernel_timeline(args.batch, args.context, args.page_size, args.layers)
     if args.workload == "sodurax":
         return sodurax_workload(args)
+    if args.workload == "memipel":
+        return memipel_workload(args)
     if args.workload != "decode":
         return serve_workload(args.workload)
     warmup = max(args.warmup, 3)

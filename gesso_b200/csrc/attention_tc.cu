@@ -92,11 +92,13 @@ __device__ __forceinline__ void load_block(KVFrag<HD>& f, const bf16* __restrict
 // keep: with a window, keys below `keep` stay visible (0: none).  PSPLIT: a probability enters the P V product
 // as the sum of two bfloat16 numbers (its rounding and the rounding of what is left), i.e. with 16 bits of
 // mantissa instead of 8, for mixers whose attention weights are to act in 32-bit precision.
+// slope_a / slope_b: the distance bias of the heads in rows g and g+8 (0: none), times log2(e).
 template <int HD, bool UPPER = true, bool PSPLIT = false>
 __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&qf)[HD / 32],
                                              const uint4 (&qg)[HD / 32], float (&o)[HD / 8][4], float (&m)[2],
                                              float (&l)[2], int key0, int t, int pos_a, int pos_b, int lo_a,
-                                             int lo_b, float scale_log2, bool need_mask, int keep = 0) {
+                                             int lo_b, float scale_log2, bool need_mask, int keep = 0,
+                                             float slope_a = 0.f, float slope_b = 0.f) {
     float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int c = 0; c < HD / 32; ++c) {
@@ -111,8 +113,9 @@ __device__ __forceinline__ void attend_block(const KVFrag<HD>& f, const uint4 (&
     const int kbase = key0 + 4 * t;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        sa[i] *= scale_log2;
-        if (UPPER) sb[i] *= scale_log2;
+        // a distance bias: slope * (query position - key position) is taken off (slopes in the base-2 domain)
+        sa[i] = sa[i] * scale_log2 - slope_a * (float)(pos_a - (kbase + i));
+        if (UPPER) sb[i] = sb[i] * scale_log2 - slope_b * (float)(pos_b - (kbase + i));
         if (need_mask) {
             const int key = kbase + i;
             if (key > pos_a || (key < lo_a && key >= keep)) sa[i] = -INFINITY;
@@ -228,7 +231,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
                         bf16* __restrict__ out, int nh, int nkv, int window, float scale_log2, int n_splits,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ tickets,
                         const int* __restrict__ kv_span, int slots, int keep, const bf16* __restrict__ gate,
-                        int gate_stride) {
+                        int gate_stride, const float* __restrict__ slopes) {
     // ring: [stage][piece][128 threads]: HD/16 pieces of 16 bytes for K, then HD/8 pieces of 8 bytes for V;
     // afterwards the same memory serves the merge of the warps ([4 warps][16 rows][HD + 2] floats)
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -349,6 +352,9 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
     float o[HD / 8][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 #pragma unroll
     for (int j = 0; j < HD / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+    // rows g and g+8 are query heads kvh * G + g and + 8
+    const float slope_a = (slopes && g < G) ? slopes[kvh * G + g] * LOG2E : 0.f;
+    const float slope_b = (slopes && UPPER && g + 8 < G) ? slopes[kvh * G + g + 8] * LOG2E : 0.f;
 
     int read_stage = 0;
 #pragma unroll 1
@@ -367,7 +373,8 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
         for (int j = 0; j < VP; ++j) cur.v[j] = *reinterpret_cast<const uint2*>(ring_mine_v + stage_off + j * 128 * 8);
         issue();                                          // refill the stage just read
         const bool need_mask = (b * 16 + 15 > pos) || (b * 16 < lo);
-        attend_block<HD, UPPER, PSPLIT>(cur, qf, qg, o, m, l, b * 16, t, pos, pos, lo, lo, scale_log2, need_mask, keep);
+        attend_block<HD, UPPER, PSPLIT>(cur, qf, qg, o, m, l, b * 16, t, pos, pos, lo, lo, scale_log2, need_mask, keep,
+                                        slope_a, slope_b);
     }
     asm volatile("cp.async.wait_group 0;\n" ::);
     __syncthreads();                                      // the ring is free: it becomes the merge buffer
@@ -456,7 +463,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
                          int page_size, const int* __restrict__ seg_start, const int* __restrict__ seg_pos0,
                          const int* __restrict__ tile_seg, const int* __restrict__ tile_q0,
                          bf16* __restrict__ out, int nh, int nkv, int window, float scale_log2, int keep,
-                         const bf16* __restrict__ gate, int gate_stride) {
+                         const bf16* __restrict__ gate, int gate_stride, const float* __restrict__ slopes) {
     // Long tiles first: the queries at the end of a prompt have the most keys to read.  Blocks are handed
     // out in the order of blockIdx.x: the (kv head, head pair) blocks of one tile are neighbours there and
     // the tiles go from the longest to the shortest, a greedy schedule by decreasing work.
@@ -511,9 +518,11 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
         // a block needs masking if some row cannot see its last key, or a window cuts into it
         const bool need_mask = (b * 16 + 15 > pos_first) || (window > 0 && b * 16 < max(lo_a, lo_b));
 #pragma unroll
-        for (int h = 0; h < HPW; ++h)
+        for (int h = 0; h < HPW; ++h) {
+            const float slope = slopes ? slopes[head0 + h] * LOG2E : 0.f;       // the rows of a warp are tokens of one head
             attend_block<HD, true, PSPLIT>(cur, qf[h], qg[h], o[h], m[h], l[h], b * 16, t, pos_a, pos_b, lo_a, lo_b,
-                                           scale_log2, need_mask, keep);
+                                           scale_log2, need_mask, keep, slope, slope);
+        }
         if (!more) break;
         cur = nxt;
         b = b_next;
@@ -559,7 +568,7 @@ GESSO_API int gesso_decode_attention(const void* q, const void* k_pages, const v
                                      void* out, int n_segs, int nh, int nkv, int hd,
                                      int window, float scale, int n_splits, float* part_o, float* part_ml,
                                      int* tickets, const int* kv_span, int keep, const void* gate, int gate_stride,
-                                     int psplit, cudaStream_t stream) {
+                                     int psplit, const float* slopes, cudaStream_t stream) {
     if (n_segs <= 0) return 0;
     if (!gesso_attention_tc_takes(hd, page_size, nh, nkv)) return GESSO_ERR_BAD_SIZE;
     const int G = nh / nkv;
@@ -594,7 +603,7 @@ GESSO_API int gesso_decode_attention(const void* q, const void* k_pages, const v
         launch_pdl(decode_attention_kernel<HD, ST, UP, PS>, grid, dim3(128), smem, stream,                  \
             (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_pages, page_size,  \
             page_shift, positions, (bf16*)out, nh, nkv, window, scale_log2, n_splits, part_o, part_ml,      \
-            tickets, kv_span, slots, keep, (const bf16*)gate, gate_stride);                                 \
+            tickets, kv_span, slots, keep, (const bf16*)gate, gate_stride, slopes);                         \
     } while (0)
 #define GO3(HD, ST, UP)                                                                                     \
     do { if (psplit) GO4(HD, ST, UP, true); else GO4(HD, ST, UP, false); } while (0)
@@ -617,7 +626,8 @@ GESSO_API int gesso_prefill_attention(const void* q, const void* k_pages, const 
                                       const int* block_table, int max_pages, int page_size, const int* seg_start,
                                       const int* seg_pos0, const int* tile_seg, const int* tile_q0, int n_tiles,
                                       void* out, int nh, int nkv, int hd, int window, float scale, int keep,
-                                      const void* gate, int gate_stride, int psplit, cudaStream_t stream) {
+                                      const void* gate, int gate_stride, int psplit, const float* slopes,
+                                      cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (!gesso_attention_tc_takes(hd, page_size, nh, nkv)) return GESSO_ERR_BAD_SIZE;
     const int G = nh / nkv;
@@ -627,7 +637,7 @@ GESSO_API int gesso_prefill_attention(const void* q, const void* k_pages, const 
     prefill_attention_kernel<HD, HPW, PS><<<dim3((unsigned)(n_tiles * nkv * (G / HPW))), 128, 0, stream>>>(  \
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_pages, page_size,       \
         seg_start, seg_pos0, tile_seg, tile_q0, (bf16*)out, nh, nkv, window, scale_log2, keep,               \
-        (const bf16*)gate, gate_stride)
+        (const bf16*)gate, gate_stride, slopes)
 #define GO(HD, HPW)                                                                                          \
     do { if (psplit) GO2(HD, HPW, true); else GO2(HD, HPW, false); } while (0)
     if (hd <= 64 && G % 2 == 0) {

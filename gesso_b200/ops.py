@@ -487,6 +487,12 @@ def paged_attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
     return out
 
 
+def _check_slopes(slopes: Optional[torch.Tensor], nh: int) -> None:
+    if slopes is not None:
+        _cuda_contig(slopes, "slopes", torch.float32)
+        _need(slopes.numel() == nh, "one slope per query head")
+
+
 def _check_gate(gate: Optional[torch.Tensor], n: int, width: int, dtype) -> int:
     """Row stride of an output gate given as a view into a wider row-major tensor (0 without a gate)."""
     if gate is None:
@@ -925,10 +931,10 @@ _lib.declare("gesso_qk_norm_rope_store_tiles", [_lib.P, _lib.P, _lib.P, _lib.F, 
 _lib.declare("gesso_attention_tc_takes", [_lib.I, _lib.I, _lib.I, _lib.I])
 _lib.declare("gesso_decode_attention", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P,
                                         _lib.I, _lib.I, _lib.I, _lib.I, _lib.I, _lib.F, _lib.I, _lib.P, _lib.P,
-                                        _lib.P, _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.P])
+                                        _lib.P, _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P])
 _lib.declare("gesso_prefill_attention", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P,
                                          _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.F, _lib.I, _lib.P,
-                                         _lib.I, _lib.I, _lib.P])
+                                         _lib.I, _lib.I, _lib.P, _lib.P])
 
 _lib.declare("gesso_sm_count", [])
 _sm_count = 0
@@ -978,15 +984,18 @@ def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
                      block_table: torch.Tensor, positions: torch.Tensor,
                      window: Optional[int], scale: float, n_splits: int,
                      workspace=None, kv_span: Optional[torch.Tensor] = None, keep_first: int = 0,
-                     gate: Optional[torch.Tensor] = None, split_weights: bool = False) -> torch.Tensor:
+                     gate: Optional[torch.Tensor] = None, split_weights: bool = False,
+                     slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Split-KV attention for a step of single tokens (token i is request i).  ``workspace`` = (part_o, part_ml, tickets) of
     sizes [segs*nh*splits*hd], [segs*nh*splits*2] float32 and [segs*nkv] int32 (zeroed once).  ``kv_span``: int32 [2]
     on the device, the longest sequence of the step and the average one: a request then uses as many of the
     ``n_splits`` pieces as the step's lengths call for (without it, all of them).  ``keep_first``, ``gate``: as
     for :func:`paged_attention_generic`.  ``split_weights``: the attention weights enter the product with the
-    values as two bfloat16 pieces each (16 bits of mantissa)."""
+    values as two bfloat16 pieces each (16 bits of mantissa).  ``slopes``: float32 [nh], a distance bias per head
+    (``slopes[h] * (i - j)`` is taken off the score)."""
     _cuda_contig(q, "q", torch.bfloat16)
     S, nh, hd = q.shape
+    _check_slopes(slopes, nh)
     gate_stride = _check_gate(gate, S, nh * hd, q.dtype)
     nkv, page_size = k_pages.shape[1], k_pages.shape[2]
     _need(k_pages.dtype == torch.bfloat16 and v_pages.dtype == torch.bfloat16, "cache pages must be bfloat16")
@@ -1008,7 +1017,7 @@ def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
         _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, _p(positions),
         _p(out), S, nh, nkv, hd, int(window or 0), float(scale), int(n_splits), _p(part_o),
         _p(part_ml), _p(tickets), _p(kv_span), int(keep_first or 0), _p(gate), gate_stride,
-        1 if split_weights else 0, _stream()), "decode_attention")
+        1 if split_weights else 0, _p(slopes), _stream()), "decode_attention")
     return out
 
 
@@ -1016,16 +1025,17 @@ def prefill_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
                       block_table: torch.Tensor, seg_start: torch.Tensor, seg_pos0: torch.Tensor,
                       tile_seg: torch.Tensor, tile_q0: torch.Tensor, window: Optional[int],
                       scale: float, keep_first: int = 0, gate: Optional[torch.Tensor] = None,
-                      split_weights: bool = False) -> torch.Tensor:
+                      split_weights: bool = False, slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
     _cuda_contig(q, "q", torch.bfloat16)
     N, nh, hd = q.shape
+    _check_slopes(slopes, nh)
     nkv, page_size = k_pages.shape[1], k_pages.shape[2]
     out = torch.empty((N, nh * hd), dtype=q.dtype, device=q.device)
     gate_stride = _check_gate(gate, N, nh * hd, q.dtype)
     _lib.check(_lib.library().gesso_prefill_attention(
         _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, _p(seg_start),
         _p(seg_pos0), _p(tile_seg), _p(tile_q0), tile_seg.numel(), _p(out), nh, nkv, hd, int(window or 0),
-        float(scale), int(keep_first or 0), _p(gate), gate_stride, 1 if split_weights else 0, _stream()),
+        float(scale), int(keep_first or 0), _p(gate), gate_stride, 1 if split_weights else 0, _p(slopes), _stream()),
         "prefill_attention")
     return out
 

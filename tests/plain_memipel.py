@@ -231,3 +231,143 @@ def forward(cfg: dict, tensors: Dict[str, torch.Tensor], tokens, fast=True, retu
         after.append(x.clone())
     logits = norm_offset(x, tensors["final.norm"].to(F64), eps) @ emb.T
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+def route_margin(z: torch.Tensor, top: int, groups: int, keep: int) -> float:
+    """How clear the choice of one token is, in units of the router's logits: the gap between the last group that
+    is kept and the first that is not, and between the last expert that is chosen and the best one that could
+    have been chosen instead (softmax keeps the order of the logits, so the gaps are taken there; a run in 16
+    bits may choose otherwise where this is tiny)."""
+    E = z.shape[0]
+    per = E // groups
+    gaps = [math.inf]
+    gz = torch.stack([z[g * per:(g + 1) * per].max() for g in range(groups)])
+    order = gz.sort(descending=True)
+    if keep < groups:
+        gaps.append(float(order.values[keep - 1] - order.values[keep]))
+    kept = set(order.indices[:keep].tolist())
+    allowed = torch.stack([z[e] for e in range(E) if e // per in kept]).sort(descending=True).values
+    if top < allowed.shape[0]:
+        gaps.append(float(allowed[top - 1] - allowed[top]))
+    return min(gaps)
+
+
+class PlainMemipel:
+    def __init__(self, cfg: dict, tensors: Dict[str, torch.Tensor]):
+        self.cfg = cfg
+        self.W = {k: v.to(F64) for k, v in tensors.items()}
+
+    @staticmethod
+    def from_dir(model_dir: str) -> "PlainMemipel":
+        import json
+        import os
+        from gesso_b200.weights.safetensors_io import read_safetensors_file
+        with open(os.path.join(model_dir, "config.json")) as f:
+            cfg = json.load(f)
+        return PlainMemipel(cfg, read_safetensors_file(os.path.join(model_dir, "model.safetensors")))
+
+    def logits(self, tokens) -> torch.Tensor:
+        return forward(self.cfg, self.W, tokens)
+
+    def stream(self, tokens) -> torch.Tensor:
+        return forward(self.cfg, self.W, tokens, return_layers=True)[1]
+
+    def margins(self, tokens) -> torch.Tensor:
+        """Per position, the least clear router choice over all layers with routed experts."""
+        eps = float(self.cfg["norm"]["eps"])
+        x = self.W["embed"][torch.as_tensor(list(tokens), dtype=torch.long)]
+        layers = forward(self.cfg, self.W, tokens, return_layers=True)[1]
+        out = torch.full((len(tokens),), math.inf, dtype=F64)
+        for i, L in enumerate(self.cfg["layers"]):
+            mlp = L.get("mlp")
+            if mlp is not None and mlp["kind"] == "moe":
+                n = norm_offset(x, self.W[f"l{i}.norm1"], eps)
+                z = n @ self.W[f"l{i}.mlp.router"].T
+                r = mlp["router"]
+                groups = r["groups"]["count"] if r.get("groups") else 1
+                keep = r["groups"]["keep"] if r.get("groups") else 1
+                for t in range(len(tokens)):
+                    out[t] = min(float(out[t]), route_margin(z[t], r["top"], groups, keep))
+            x = layers[i]
+        return out
+
+    def greedy(self, prompt, n_new: int):
+        ids = list(prompt)
+        for _ in range(n_new):
+            ids.append(int(self.logits(ids)[-1].argmax()))
+        return ids
+
+
+# ---- random models for the tests -----------------------------------------------------------------------
+def random_tensors(cfg: dict, seed: int) -> Dict[str, torch.Tensor]:
+    """Tensors under their checkpoint names, rounded to bfloat16 (every run type sees the same numbers), drawn so
+    that nothing is flat: projections N(0, 1/fan_in) scaled up, norm offsets around zero, biases, taps and sinks
+    of order 0.3 to 1, mixing weights between 0.2 and 0.8."""
+    g = torch.Generator().manual_seed(seed)
+    W: Dict[str, torch.Tensor] = {}
+
+    def rnd(*shape, std=1.0):
+        return (torch.randn(*shape, generator=g) * std).to(torch.bfloat16)
+
+    def mat(rows, cols, gain=1.5):
+        return rnd(rows, cols, std=gain / math.sqrt(cols))
+
+    Wd, V = cfg["width"], cfg["vocab"]
+    W["embed"] = rnd(V, Wd)
+    W["final.norm"] = rnd(Wd, std=0.2)
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        W[p + "norm1"] = rnd(Wd, std=0.2)
+        H, D = m["heads"], m["dim"]
+        Dv = m.get("vdim", D)
+        if L["type"] == "latent_attention":
+            Rq, R = m["q_rank"], m["kv_rank"]
+            W[p + "mix.dq"], W[p + "mix.dkv"] = mat(Rq, Wd), mat(R, Wd)
+            W[p + "mix.dq.norm"] = (1 + 0.2 * torch.randn(Rq, generator=g)).to(torch.bfloat16)
+            W[p + "mix.dkv.norm"] = (1 + 0.2 * torch.randn(R, generator=g)).to(torch.bfloat16)
+            W[p + "mix.uq"], W[p + "mix.uk"], W[p + "mix.uv"] = mat(H * D, Rq), mat(H * D, R), mat(H * Dv, R)
+            W[p + "mix.sink"] = rnd(H, std=1.5)
+            W[p + "mix.o"] = mat(Wd, H * Dv)
+        elif L["type"] == "attention":
+            G = m.get("kv_heads", H)
+            for n, rows in (("q", H * D), ("k", G * D), ("v", G * Dv)):
+                W[p + "mix." + n] = mat(rows, Wd)
+                W[p + "mix." + n + ".b"] = rnd(rows, std=0.3)
+                if m.get("conv"):
+                    W[p + "mix." + n + ".conv"] = rnd(rows, m["conv"], std=0.7)
+            if m.get("v_mix"):
+                W[p + "mix.vmix"] = (0.2 + 0.6 * torch.rand((), generator=g)).to(torch.bfloat16)
+            W[p + "mix.o"] = mat(Wd, H * Dv)
+            W[p + "mix.o.b"] = rnd(Wd, std=0.3)
+        else:
+            W[p + "mix.q"], W[p + "mix.k"] = mat(H * D, Wd), mat(H * D, Wd)
+            W[p + "mix.v"], W[p + "mix.g"] = mat(H * Dv, Wd), mat(H * Dv, Wd)
+            W[p + "mix.norm"] = (1 + 0.2 * torch.randn(H * Dv, generator=g)).to(torch.bfloat16)
+            W[p + "mix.o"] = mat(Wd, H * Dv)
+        mlp = L.get("mlp")
+        if mlp is None:
+            continue
+        if mlp["kind"] == "dense":
+            W[p + "mlp.up"], W[p + "mlp.down"] = mat(mlp["ff"], Wd), mat(Wd, mlp["ff"])
+        else:
+            F = mlp["expert"]["ff"]
+            W[p + "mlp.router"] = mat(mlp["router"]["experts"], Wd, 3.0)
+            names = [f"e{e}" for e in range(mlp["router"]["experts"])]
+            sizes = [F] * len(names)
+            if mlp.get("shared"):
+                names.append("shared")
+                sizes.append(mlp["shared"]["ff"])
+            for n, f in zip(names, sizes):      # gains that make the clamps bite now and then
+                W[f"{p}mlp.{n}.gate"], W[f"{p}mlp.{n}.up"] = mat(f, Wd, 2.0), mat(f, Wd, 2.0)
+                W[f"{p}mlp.{n}.down"] = mat(Wd, f)
+    return W
+
+
+def write_model(model_dir: str, cfg: dict, seed: int) -> None:
+    import json
+    import os
+    from gesso_b200.weights.safetensors_io import write_safetensors_file
+    os.makedirs(model_dir, exist_ok=True)
+    with open(os.path.join(model_dir, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    write_safetensors_file(os.path.join(model_dir, "model.safetensors"), random_tensors(cfg, seed))
