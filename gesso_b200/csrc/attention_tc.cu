@@ -231,7 +231,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
                         bf16* __restrict__ out, int nh, int nkv, int window, float scale_log2, int n_splits,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int* __restrict__ tickets,
                         const int* __restrict__ kv_span, int slots, int keep, const bf16* __restrict__ gate,
-                        int gate_stride, const float* __restrict__ slopes) {
+                        int gate_stride, const float* __restrict__ slopes, const float* __restrict__ sink) {
     // ring: [stage][piece][128 threads]: HD/16 pieces of 16 bytes for K, then HD/8 pieces of 8 bytes for V;
     // afterwards the same memory serves the merge of the warps ([4 warps][16 rows][HD + 2] floats)
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -413,6 +413,8 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
         }
         const int head = kvh * G + r;
         if (used == 1) {
+            // a sink: one more term exp(sink) in the denominator, with no key and no value (base-2 domain here)
+            if (sink) L += exp2f(sink[head] * LOG2E - M);
             out[((size_t)tok * nh + head) * HD + d] =
                 __float2bfloat16_rn(acc / L * gate_of(gate, (size_t)tok * gate_stride + (size_t)head * HD + d));
         } else {
@@ -447,6 +449,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
             L += __ldcg(part_ml + (p0 + s) * 2 + 1) * f;
             acc += __ldcg(part_o + (p0 + s) * HD + d) * f;
         }
+        if (sink) L += exp2f(sink[head] * LOG2E - M);      // once, where the pieces come together
         out[((size_t)tok * nh + head) * HD + d] =
             __float2bfloat16_rn(acc / L * gate_of(gate, (size_t)tok * gate_stride + (size_t)head * HD + d));
     }
@@ -463,7 +466,8 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
                          int page_size, const int* __restrict__ seg_start, const int* __restrict__ seg_pos0,
                          const int* __restrict__ tile_seg, const int* __restrict__ tile_q0,
                          bf16* __restrict__ out, int nh, int nkv, int window, float scale_log2, int keep,
-                         const bf16* __restrict__ gate, int gate_stride, const float* __restrict__ slopes) {
+                         const bf16* __restrict__ gate, int gate_stride, const float* __restrict__ slopes,
+                         const float* __restrict__ sink) {
     // Long tiles first: the queries at the end of a prompt have the most keys to read.  Blocks are handed
     // out in the order of blockIdx.x: the (kv head, head pair) blocks of one tile are neighbours there and
     // the tiles go from the longest to the shortest, a greedy schedule by decreasing work.
@@ -529,7 +533,11 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
     }
 #pragma unroll
     for (int h = 0; h < HPW; ++h) {
-        const float la = quad_sum(l[h][0]), lb = quad_sum(l[h][1]);
+        float la = quad_sum(l[h][0]), lb = quad_sum(l[h][1]);
+        if (sink) {        // one more term exp(sink) in the denominator (the running maxima are finite: a row sees itself)
+            la += exp2f(sink[head0 + h] * LOG2E - m[h][0]);
+            lb += exp2f(sink[head0 + h] * LOG2E - m[h][1]);
+        }
         const float ia = 1.f / la, ib = 1.f / lb;
         bf16* oa = out + ((size_t)(t0 + q0 + g) * nh + head0 + h) * HD + 2 * t;
         bf16* ob = out + ((size_t)(t0 + q0 + g + 8) * nh + head0 + h) * HD + 2 * t;
@@ -568,7 +576,7 @@ GESSO_API int gesso_decode_attention(const void* q, const void* k_pages, const v
                                      void* out, int n_segs, int nh, int nkv, int hd,
                                      int window, float scale, int n_splits, float* part_o, float* part_ml,
                                      int* tickets, const int* kv_span, int keep, const void* gate, int gate_stride,
-                                     int psplit, const float* slopes, cudaStream_t stream) {
+                                     int psplit, const float* slopes, const float* sink, cudaStream_t stream) {
     if (n_segs <= 0) return 0;
     if (!gesso_attention_tc_takes(hd, page_size, nh, nkv)) return GESSO_ERR_BAD_SIZE;
     const int G = nh / nkv;
@@ -603,7 +611,7 @@ GESSO_API int gesso_decode_attention(const void* q, const void* k_pages, const v
         launch_pdl(decode_attention_kernel<HD, ST, UP, PS>, grid, dim3(128), smem, stream,                  \
             (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_pages, page_size,  \
             page_shift, positions, (bf16*)out, nh, nkv, window, scale_log2, n_splits, part_o, part_ml,      \
-            tickets, kv_span, slots, keep, (const bf16*)gate, gate_stride, slopes);                         \
+            tickets, kv_span, slots, keep, (const bf16*)gate, gate_stride, slopes, sink);                   \
     } while (0)
 #define GO3(HD, ST, UP)                                                                                     \
     do { if (psplit) GO4(HD, ST, UP, true); else GO4(HD, ST, UP, false); } while (0)
@@ -627,7 +635,7 @@ GESSO_API int gesso_prefill_attention(const void* q, const void* k_pages, const 
                                       const int* seg_pos0, const int* tile_seg, const int* tile_q0, int n_tiles,
                                       void* out, int nh, int nkv, int hd, int window, float scale, int keep,
                                       const void* gate, int gate_stride, int psplit, const float* slopes,
-                                      cudaStream_t stream) {
+                                      const float* sink, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (!gesso_attention_tc_takes(hd, page_size, nh, nkv)) return GESSO_ERR_BAD_SIZE;
     const int G = nh / nkv;
@@ -637,7 +645,7 @@ GESSO_API int gesso_prefill_attention(const void* q, const void* k_pages, const 
     prefill_attention_kernel<HD, HPW, PS><<<dim3((unsigned)(n_tiles * nkv * (G / HPW))), 128, 0, stream>>>(  \
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, block_table, max_pages, page_size,       \
         seg_start, seg_pos0, tile_seg, tile_q0, (bf16*)out, nh, nkv, window, scale_log2, keep,               \
-        (const bf16*)gate, gate_stride, slopes)
+        (const bf16*)gate, gate_stride, slopes, sink)
 #define GO(HD, HPW)                                                                                          \
     do { if (psplit) GO2(HD, HPW, true); else GO2(HD, HPW, false); } while (0)
     if (hd <= 64 && G % 2 == 0) {

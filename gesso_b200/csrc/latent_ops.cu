@@ -6,7 +6,10 @@
 //    cq [N, Rq] (the operand of the up projection); the key/value latent c is the ONLY thing a position leaves in
 //    the cache: it is written to the position's slot of the K pages ([page][1][slot][Rkv]).  Either piece may be
 //    absent (Rq = 0: queries without a latent; write_kv = 0: an entry that reads another entry's cache).
-//    One warp per token.
+//    With `v_pages` the latent is also written transposed ([page][1][Rkv][slot]), the layout from which the
+//    tensor-core attention kernels read values; the token that ends a request's portion then zeroes the slots
+//    behind its own up to the end of its 16-slot block (those kernels multiply masked weights, exact zeros, with
+//    whatever such a slot holds, and pages pass from request to request as they are).  One warp per token.
 //
 // 2. headwise_linear: out[n, h, o] = sum_i W[h, i, o] x[n, h, i] for per-head matrices W [H, I, O] (input-major, so
 //    that the threads of a block, one per output, read neighbouring elements).  Latent
@@ -22,7 +25,8 @@ latent_norm_store_kernel(const float* __restrict__ p, int Rq, int Rkv, const flo
                          const float* __restrict__ wkv, float eps, TO* __restrict__ cq,
                          const int* __restrict__ positions, const int* __restrict__ seg_of_token,
                          const int* __restrict__ block_table, int max_pages, int page_size,
-                         TO* __restrict__ k_pages, int write_kv, int* __restrict__ status, int n_tokens) {
+                         TO* __restrict__ k_pages, int write_kv, int* __restrict__ status, int n_tokens,
+                         TO* __restrict__ v_pages) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
@@ -48,24 +52,36 @@ latent_norm_store_kernel(const float* __restrict__ p, int Rq, int Rkv, const flo
             if (lane == 0) atomicExch(status, 1);
             return;
         }
-        TO* dst = k_pages + ((size_t)page * page_size + (pos % page_size)) * Rkv;
+        const int slot = pos % page_size;
+        TO* dst = k_pages + ((size_t)page * page_size + slot) * Rkv;
         for (int j = lane; j < Rkv; j += 32) dst[j] = from_f32<TO>((r2[j] / denom) * wkv[j]);
+        if (v_pages) {
+            const bool last = t == n_tokens - 1 || seg_of_token[t + 1] != seg_of_token[t];
+            const int clear = last ? min(page_size, ((slot >> 4) + 1) << 4) - slot : 1;
+            TO* vt = v_pages + (size_t)page * Rkv * page_size + slot;
+            for (int j = lane; j < Rkv; j += 32) {
+                vt[(size_t)j * page_size] = from_f32<TO>((r2[j] / denom) * wkv[j]);
+                for (int z = 1; z < clear; ++z) vt[(size_t)j * page_size + z] = from_f32<TO>(0.f);
+            }
+        }
     }
 }
 
 GESSO_API int gesso_latent_norm_store(const float* p, int Rq, int Rkv, const float* wq, const float* wkv, float eps,
                                       void* cq, int dtype, const int* positions, const int* seg_of_token,
                                       const int* block_table, int max_pages, int page_size, void* k_pages,
-                                      int write_kv, int* status, int n_tokens, cudaStream_t stream) {
+                                      int write_kv, int* status, int n_tokens, void* v_pages, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (Rq < 0 || Rkv < 0 || Rq + Rkv <= 0 || page_size <= 0) return GESSO_ERR_BAD_SIZE;
     const dim3 grid((n_tokens + 3) / 4);
     if (dtype == GESSO_F32)
         launch_pdl(latent_norm_store_kernel<float>, grid, dim3(128), 0, stream, p, Rq, Rkv, wq, wkv, eps, (float*)cq,
-                   positions, seg_of_token, block_table, max_pages, page_size, (float*)k_pages, write_kv, status, n_tokens);
+                   positions, seg_of_token, block_table, max_pages, page_size, (float*)k_pages, write_kv, status, n_tokens,
+                   (float*)v_pages);
     else if (dtype == GESSO_BF16)
         launch_pdl(latent_norm_store_kernel<bf16>, grid, dim3(128), 0, stream, p, Rq, Rkv, wq, wkv, eps, (bf16*)cq,
-                   positions, seg_of_token, block_table, max_pages, page_size, (bf16*)k_pages, write_kv, status, n_tokens);
+                   positions, seg_of_token, block_table, max_pages, page_size, (bf16*)k_pages, write_kv, status, n_tokens,
+                   (bf16*)v_pages);
     else
         return GESSO_ERR_BAD_DTYPE;
     return launch_status();

@@ -40,7 +40,7 @@ _SIGNATURES = {
     "gesso_gelu_erf": [P, P, I, LL, P],
     "gesso_glu_clamped": [P, P, I, I, I, I, F, F, P],
     "gesso_causal_conv": [P, I, I, P, P, P, LL, P, P, P, P, I, I, I, I, P, I, I, I, F, P],
-    "gesso_latent_norm_store": [P, I, I, P, P, F, P, I, P, P, P, I, I, P, I, P, I, P],
+    "gesso_latent_norm_store": [P, I, I, P, P, F, P, I, P, P, P, I, I, P, I, P, I, P, P],
     "gesso_headwise_linear": [P, I, P, I, P, I, I, I, I, I, P],
     "gesso_lightning": [P, I, I, P, LL, P, P, P, P, I, I, I, I, I, P],
     "gesso_gated_rmsnorm": [P, P, F, P, I, P, I, I, I, P],

@@ -4,9 +4,8 @@ float32 runs always take the FP32-arithmetic kernel.  bfloat16 runs take the ten
 when the sizes fit them (head 32/64/96/128, pages in multiples of 16 slots): the split-KV kernel
 for steps of single tokens; for steps with portions the tcgen05 flash kernel (head 64, 2 to 16 query
 heads per kv head) or else the mma.sync flash kernel; other sizes take the FP32-arithmetic kernel
-on bfloat16 data.  A distance bias per head is taken by the mma.sync kernels and the FP32-arithmetic kernel; a sink
-in the softmax denominator, values that are the keys themselves and float32 queries by the FP32-arithmetic kernel
-only.  Kept first keys under a window, an output gate and attention weights in two
+on bfloat16 data.  A distance bias per head and a sink in the softmax denominator are taken by the mma.sync kernels and the
+FP32-arithmetic kernel; values that are the keys themselves and float32 queries by the FP32-arithmetic kernel only.  Kept first keys under a window, an output gate and attention weights in two
 bfloat16 pieces are taken by every kernel (the FP32-arithmetic kernel's weights are float32 anyway);
 values of another width than the keys by the FP32-arithmetic kernel only.  Every
 branch is one of this library's own kernels.
@@ -25,11 +24,11 @@ def paged_attention(rt, q, cache, ctx, window, scale, keep_first: int = 0, gate=
     vd = cache.v_pages.shape[2]
     if window is None:
         keep_first = 0                       # without a window every earlier key is visible anyway
-    # A distance bias on the scores: the mma.sync kernels take it (head 32/64/96/128, values as wide as keys), the
-    # tcgen05 kernel does not.  A sink in the denominator, values that are the keys themselves (latent attention,
-    # absorbed) and float32 queries: the FP32-arithmetic kernel takes them all.
-    plain_softmax = sink is None and not values_are_keys
-    if not plain_softmax or (slopes is not None and not (
+    # A distance bias on the scores and a sink in the denominator: the mma.sync kernels take them (head 32/64/96/128,
+    # values as wide as keys), the tcgen05 kernel does not.  Values that are the keys themselves (latent attention
+    # without transposed pages) and float32 queries: the FP32-arithmetic kernel takes them all.
+    special = sink is not None or slopes is not None
+    if values_are_keys or q.dtype != cache.k_pages.dtype or (special and not (
             q.dtype == torch.bfloat16 and vd == hd and ops.fast_attention_takes(hd, page_size, nh, nkv))):
         return ops.paged_attention_generic(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions,
                                            ctx.seg_of_token, window, scale, keep_first, gate, sink=sink, slopes=slopes,
@@ -50,14 +49,14 @@ def paged_attention(rt, q, cache, ctx, window, scale, keep_first: int = 0, gate=
                     rt.shared[key] = ws
             return ops.decode_attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.positions,
                                         window, scale, splits, ws, ctx.kv_span, keep_first, gate, split_weights,
-                                        slopes=slopes)
-        if slopes is None and ops.attention_tcgen05_takes(hd, page_size, nh, nkv):
+                                        slopes=slopes, sink=sink)
+        if not special and ops.attention_tcgen05_takes(hd, page_size, nh, nkv):
             # head 64 with 2..16 query heads per kv head: S and P in tensor memory, pages by TMA
             return ops.prefill_attention_tcgen05(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.seg_start,
                                                  ctx.seg_pos0, ctx.tile_seg, ctx.tile_q0, window, scale, keep_first, gate,
                                                  split_weights)
         return ops.prefill_attention(q, cache.k_pages, cache.v_pages, cache.block_table, ctx.seg_start,
                                      ctx.seg_pos0, ctx.tile_seg, ctx.tile_q0, window, scale, keep_first, gate,
-                                     split_weights, slopes=slopes)
+                                     split_weights, slopes=slopes, sink=sink)
     return ops.paged_attention_generic(q, cache.k_pages, cache.v_pages, cache.block_table,
                                        ctx.positions, ctx.seg_of_token, window, scale, keep_first, gate)

@@ -490,7 +490,7 @@ def paged_attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
 def _check_slopes(slopes: Optional[torch.Tensor], nh: int) -> None:
     if slopes is not None:
         _cuda_contig(slopes, "slopes", torch.float32)
-        _need(slopes.numel() == nh, "one slope per query head")
+        _need(slopes.numel() == nh, "one value per query head")
 
 
 def _check_gate(gate: Optional[torch.Tensor], n: int, width: int, dtype) -> int:
@@ -538,13 +538,18 @@ def causal_conv(u: torch.Tensor, n_channels: int, bias: Optional[torch.Tensor], 
     return out
 
 
+# GESSO_LATENT_TC=0 keeps latent attention on the FP32-arithmetic kernel whatever its sizes (to measure the difference).
+LATENT_TENSOR_CORES = os.environ.get("GESSO_LATENT_TC", "1") != "0"
+
+
 def latent_norm_store(proj: torch.Tensor, q_rank: int, kv_rank: int, wq: Optional[torch.Tensor],
                       wkv: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype, positions: torch.Tensor,
                       seg_of_token: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor, write_kv: bool,
-                      status: torch.Tensor) -> Optional[torch.Tensor]:
+                      status: torch.Tensor, v_pages: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """RMS-norm the two latents of the fused down projection ``proj`` (float32 [N, q_rank + kv_rank]) with their
     weights; returns the query latent [N, q_rank] in ``out_dtype`` and writes the key/value latent into the
-    position's slot of ``k_pages`` ([pages, 1, page size, kv_rank])."""
+    position's slot of ``k_pages`` ([pages, 1, page size, kv_rank]) and, with ``v_pages`` ([pages, 1, kv_rank, page
+    size]), transposed into those too (the layout the tensor-core attention kernels read values from)."""
     _cuda_contig(proj, "proj", torch.float32)
     N = proj.shape[0]
     _need(proj.shape[1] == q_rank + kv_rank, "the fused projection must hold the two latents side by side")
@@ -555,11 +560,17 @@ def latent_norm_store(proj: torch.Tensor, q_rank: int, kv_rank: int, wq: Optiona
     _need(k_pages.is_contiguous() and k_pages.dtype == out_dtype and k_pages.dim() == 4 and k_pages.shape[1] == 1
           and (not write_kv or k_pages.shape[3] == kv_rank),
           "latent pages must be [pages, 1, page size, kv_rank] of the run dtype")
+    if v_pages is not None and v_pages.numel() == 0:
+        v_pages = None
+    if v_pages is not None:
+        _need(v_pages.is_contiguous() and v_pages.dtype == out_dtype and
+              tuple(v_pages.shape) == (k_pages.shape[0], 1, kv_rank, k_pages.shape[2]),
+              "transposed latent pages must be [pages, 1, kv_rank, page size] of the run dtype")
     cq = torch.empty((N, q_rank), dtype=out_dtype, device=proj.device) if q_rank else None
     _lib.check(_lib.library().gesso_latent_norm_store(
         _p(proj), int(q_rank), int(kv_rank), _p(wq), _p(wkv), float(eps), _p(cq), _dt(k_pages), _p(positions),
         _p(seg_of_token), _p(block_table), block_table.shape[1], k_pages.shape[2], _p(k_pages), 1 if write_kv else 0,
-        _p(status), N, _stream()), "latent_norm_store")
+        _p(status), N, _p(v_pages) if write_kv else None, _stream()), "latent_norm_store")
     return cq
 
 
@@ -931,10 +942,10 @@ _lib.declare("gesso_qk_norm_rope_store_tiles", [_lib.P, _lib.P, _lib.P, _lib.F, 
 _lib.declare("gesso_attention_tc_takes", [_lib.I, _lib.I, _lib.I, _lib.I])
 _lib.declare("gesso_decode_attention", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P,
                                         _lib.I, _lib.I, _lib.I, _lib.I, _lib.I, _lib.F, _lib.I, _lib.P, _lib.P,
-                                        _lib.P, _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P])
+                                        _lib.P, _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P])
 _lib.declare("gesso_prefill_attention", [_lib.P, _lib.P, _lib.P, _lib.P, _lib.I, _lib.I, _lib.P, _lib.P, _lib.P,
                                          _lib.P, _lib.I, _lib.P, _lib.I, _lib.I, _lib.I, _lib.I, _lib.F, _lib.I, _lib.P,
-                                         _lib.I, _lib.I, _lib.P, _lib.P])
+                                         _lib.I, _lib.I, _lib.P, _lib.P, _lib.P])
 
 _lib.declare("gesso_sm_count", [])
 _sm_count = 0
@@ -985,17 +996,19 @@ def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
                      window: Optional[int], scale: float, n_splits: int,
                      workspace=None, kv_span: Optional[torch.Tensor] = None, keep_first: int = 0,
                      gate: Optional[torch.Tensor] = None, split_weights: bool = False,
-                     slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     slopes: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Split-KV attention for a step of single tokens (token i is request i).  ``workspace`` = (part_o, part_ml, tickets) of
     sizes [segs*nh*splits*hd], [segs*nh*splits*2] float32 and [segs*nkv] int32 (zeroed once).  ``kv_span``: int32 [2]
     on the device, the longest sequence of the step and the average one: a request then uses as many of the
     ``n_splits`` pieces as the step's lengths call for (without it, all of them).  ``keep_first``, ``gate``: as
     for :func:`paged_attention_generic`.  ``split_weights``: the attention weights enter the product with the
     values as two bfloat16 pieces each (16 bits of mantissa).  ``slopes``: float32 [nh], a distance bias per head
-    (``slopes[h] * (i - j)`` is taken off the score)."""
+    (``slopes[h] * (i - j)`` is taken off the score).  ``sink``: float32 [nh], one more term ``exp(sink[h])`` in the
+    softmax denominator."""
     _cuda_contig(q, "q", torch.bfloat16)
     S, nh, hd = q.shape
     _check_slopes(slopes, nh)
+    _check_slopes(sink, nh)
     gate_stride = _check_gate(gate, S, nh * hd, q.dtype)
     nkv, page_size = k_pages.shape[1], k_pages.shape[2]
     _need(k_pages.dtype == torch.bfloat16 and v_pages.dtype == torch.bfloat16, "cache pages must be bfloat16")
@@ -1017,7 +1030,7 @@ def decode_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
         _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, _p(positions),
         _p(out), S, nh, nkv, hd, int(window or 0), float(scale), int(n_splits), _p(part_o),
         _p(part_ml), _p(tickets), _p(kv_span), int(keep_first or 0), _p(gate), gate_stride,
-        1 if split_weights else 0, _p(slopes), _stream()), "decode_attention")
+        1 if split_weights else 0, _p(slopes), _p(sink), _stream()), "decode_attention")
     return out
 
 
@@ -1025,17 +1038,19 @@ def prefill_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
                       block_table: torch.Tensor, seg_start: torch.Tensor, seg_pos0: torch.Tensor,
                       tile_seg: torch.Tensor, tile_q0: torch.Tensor, window: Optional[int],
                       scale: float, keep_first: int = 0, gate: Optional[torch.Tensor] = None,
-                      split_weights: bool = False, slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      split_weights: bool = False, slopes: Optional[torch.Tensor] = None,
+                      sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     _cuda_contig(q, "q", torch.bfloat16)
     N, nh, hd = q.shape
     _check_slopes(slopes, nh)
+    _check_slopes(sink, nh)
     nkv, page_size = k_pages.shape[1], k_pages.shape[2]
     out = torch.empty((N, nh * hd), dtype=q.dtype, device=q.device)
     gate_stride = _check_gate(gate, N, nh * hd, q.dtype)
     _lib.check(_lib.library().gesso_prefill_attention(
         _p(q), _p(k_pages), _p(v_pages), _p(block_table), block_table.shape[1], page_size, _p(seg_start),
         _p(seg_pos0), _p(tile_seg), _p(tile_q0), tile_seg.numel(), _p(out), nh, nkv, hd, int(window or 0),
-        float(scale), int(keep_first or 0), _p(gate), gate_stride, 1 if split_weights else 0, _p(slopes), _stream()),
+        float(scale), int(keep_first or 0), _p(gate), gate_stride, 1 if split_weights else 0, _p(slopes), _p(sink), _stream()),
         "prefill_attention")
     return out
 

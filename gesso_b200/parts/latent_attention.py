@@ -17,6 +17,12 @@ no value pages.  The engine evaluates the *absorbed* form, which reads the cache
 
 so that a step never expands keys and values of cached positions, whether it decodes or reads a prompt.
 
+In bfloat16 runs whose sizes the tensor-core attention kernels take (``kv_rank`` 32, 64, 96 or 128, at most 16
+heads) the latent is cached twice, as rows and transposed (the two layouts those kernels read keys and values
+from; still ``2 kv_rank`` numbers per position against ``H (head_dim + v_head_dim)`` of expanded keys and values),
+q' is rounded to bfloat16 as their operand, and the attention weights act on the latents as two bfloat16 pieces.
+Every other size and the float32 run keep one copy and take the FP32-arithmetic kernel with float32 q'.
+
 Parameters: hidden_size, n_heads, head_dim, v_head_dim, q_rank, kv_rank, scale, window (``None``: all keys), sink
 (default true), norm_eps.  Tensors: ``dq.weight`` [q_rank, hidden], ``dq_norm.weight`` [q_rank], ``uq.weight`` [H *
 head_dim, q_rank], ``dkv.weight`` [kv_rank, hidden], ``dkv_norm.weight`` [kv_rank], ``uk.weight`` [H * head_dim,
@@ -56,6 +62,7 @@ class LatentAttention(Mixer):
             raise invalid(f"latent attention: kv_rank {self.kv_rank} is above 256, the most the attention kernel takes")
         if self.window is not None and int(self.window) < 1:
             raise invalid("latent attention: window must be >= 1")
+        self.mirror = False       # decided when the weights are bound (the run type decides)
 
     def param_decls(self) -> Dict[str, ParamDecl]:
         H, D, Dv, Rq, R, W = self.nh, self.hd, self.vd, self.q_rank, self.kv_rank, self.hidden
@@ -74,8 +81,10 @@ class LatentAttention(Mixer):
         return d
 
     def cache_need(self):
-        # one latent per position: a single kv head of kv_rank features, and no value pages
-        return PagedNeed(1, self.kv_rank, int(self.window) if self.window is not None else None, 0, 0)
+        # one latent per position: a single kv head of kv_rank features; no value pages, or (for the tensor-core
+        # kernels) the same latent once more, transposed
+        return PagedNeed(1, self.kv_rank, int(self.window) if self.window is not None else None, 0,
+                         None if self.mirror else 0)
 
     def bind(self, tensors, rt) -> None:
         H, D, Dv, R = self.nh, self.hd, self.vd, self.kv_rank
@@ -91,16 +100,23 @@ class LatentAttention(Mixer):
         self.sink = tensors["sink"].float().contiguous() if self.has_sink else None
         self.w_o = tensors["o_proj.weight"]
         self.rt = rt
+        self.mirror = (rt.dtype == torch.bfloat16 and self.kv_rank in (32, 64, 96, 128) and self.nh <= 16
+                       and ops.LATENT_TENSOR_CORES)
 
     def forward(self, x, ctx, cache):
         writes = cache.writes
         Rq, R = self.q_rank, self.kv_rank
         proj = ops.linear(x, self.w_down if writes else self.w_dq, out_dtype=torch.float32)
         cq = ops.latent_norm_store(proj, Rq, R if writes else 0, self.wn_q, self.wn_kv, self.eps, x.dtype,
-                                   ctx.positions, ctx.seg_of_token, cache.block_table, cache.k_pages, writes, ctx.status)
+                                   ctx.positions, ctx.seg_of_token, cache.block_table, cache.k_pages, writes, ctx.status,
+                                   v_pages=cache.v_pages if self.mirror else None)
         q = ops.linear(cq, self.w_uq, out_dtype=x.dtype).view(-1, self.nh, self.hd)
-        q_lat = ops.headwise_linear(q, self.w_absorb, torch.float32)                      # [N, H, R]
-        a = self.rt.attention(q_lat, cache, ctx, self.window, self.scale, sink=self.sink, values_are_keys=True)
+        if self.mirror:
+            q_lat = ops.headwise_linear(q, self.w_absorb, x.dtype)                        # [N, H, R], an operand
+            a = self.rt.attention(q_lat, cache, ctx, self.window, self.scale, sink=self.sink, split_weights=True)
+        else:
+            q_lat = ops.headwise_linear(q, self.w_absorb, torch.float32)                  # [N, H, R]
+            a = self.rt.attention(q_lat, cache, ctx, self.window, self.scale, sink=self.sink, values_are_keys=True)
         o = ops.headwise_linear(a.view(-1, self.nh, R), self.w_expand, x.dtype)           # [N, H, Dv]
         return ops.linear(o.view(-1, self.nh * self.vd), self.w_o, out_dtype=torch.float32), None
 

@@ -274,16 +274,22 @@ def test_attention_sink_bias_and_edges_stand_out(kind, H, G, D, Vd, window, dtyp
 
 @pytest.mark.parametrize("H,G,D,window", [(8, 2, 64, 45), (4, 4, 128, 64), (4, 2, 32, None), (6, 2, 96, 37), (16, 1, 64, 130),
                                           (32, 2, 64, 50)])
-def test_distance_bias_on_the_tensor_core_kernels(H, G, D, window):
+@pytest.mark.parametrize("what", ["bias", "sink"])
+def test_distance_bias_and_sink_on_the_tensor_core_kernels(H, G, D, window, what):
     """The sizes whose bfloat16 steps take the mma.sync kernels (a portion; single tokens with the keys cut into
-    pieces or not): the same stand-out keys as above, through the engine's own choice of kernel."""
+    pieces or not): the same stand-out keys as above, through the engine's own choice of kernel, with a distance
+    bias per head or with sinks (one of them far above every score)."""
     from gesso_b200.engine import attention_dispatch
     from gesso_b200.engine.model import PagedView, Runtime
     T, page, scale = 330, 16, 0.17
     q = torch.randn(T, H, D, device=DEV)
     k = torch.randn(T, G, D, device=DEV)
     v = torch.randn(T, G, D, device=DEV)
-    slopes = pm.alibi_slopes(H).float().to(DEV)
+    slopes = pm.alibi_slopes(H).float().to(DEV) if what == "bias" else None
+    sink = None
+    if what == "sink":
+        sink = torch.randn(H, device=DEV)
+        sink[0] = 9.0
     tests = (T - 1, 100, 77)
     for i in tests:
         edges = [0, i // 2] if window is None else [i - window + 1, i - window]
@@ -294,7 +300,8 @@ def test_distance_bias_on_the_tensor_core_kernels(H, G, D, window):
     order = list(range(21))[::-1]
     kp, vp, bt = _pages(k, v, page, order)
     vp = torch.nan_to_num(vp)                       # the cache writer keeps the tail of a request's last block zero
-    want = pm.attend_fast(q.double().cpu(), k.double().cpu(), v.double().cpu(), scale, window, slopes=slopes.double().cpu(),
+    want = pm.attend_fast(q.double().cpu(), k.double().cpu(), v.double().cpu(), scale, window,
+                          sink=None if sink is None else sink.cpu(), slopes=None if slopes is None else slopes.double().cpu(),
                           group=H // G)
     rt = Runtime(DEV, torch.bfloat16, 1024)
 
@@ -309,7 +316,8 @@ def test_distance_bias_on_the_tensor_core_kernels(H, G, D, window):
     c.tile_seg = torch.zeros(tiles, dtype=torch.int32, device=DEV)
     c.tile_q0 = torch.arange(tiles, dtype=torch.int32, device=DEV) * 64
     c.kv_span = i32([T, T])
-    got = attention_dispatch.paged_attention(rt, q, PagedView(kp, vp, bt, True), c, window, scale, slopes=slopes).double().cpu()
+    got = attention_dispatch.paged_attention(rt, q, PagedView(kp, vp, bt, True), c, window, scale, slopes=slopes, sink=sink,
+                                             split_weights=True).double().cpu()
     err = (got - want).abs().max() / want.abs().max()
     assert err <= 2e-2, f"portion: {float(err):.3e}"
     for i in tests + (0, 16, 15, 300):
@@ -320,7 +328,7 @@ def test_distance_bias_on_the_tensor_core_kernels(H, G, D, window):
         if window:
             bt_i[0, :max(0, i - window + 1) // page] = -1
         got = attention_dispatch.paged_attention(rt, q[i:i + 1].contiguous(), PagedView(kp, vp, bt_i, True), c, window, scale,
-                                                 slopes=slopes).double().cpu()
+                                                 slopes=slopes, sink=sink, split_weights=True).double().cpu()
         err = (got[0] - want[i]).abs().max() / want.abs().max()
         assert err <= 2e-2, f"single token at {i}: {float(err):.3e}"
 

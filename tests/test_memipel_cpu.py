@@ -44,7 +44,7 @@ def test_cache_plan_pages_and_states():
     spec = spec_from_config(cm.MMP_A)
     plan = CachePlan(spec, [build_block(b) for b in spec.blocks])
     needs = [need for need, _ in plan.paged_groups]
-    assert PagedNeed(1, 32, 20, 0, 0) in needs                        # the latent alone, no value pages
+    assert PagedNeed(1, 32, 20, 0, 0) in needs                        # the latent alone, no value pages (parts not bound)
     assert PagedNeed(2, 16, 37, 0, None) in needs and PagedNeed(1, 32, 9, 0, None) in needs
     states = [need for need, _ in plan.state_entries]
     assert StateNeed((2, 24, 16), "float32") in states                # heads x value size x key size
