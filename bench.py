@@ -605,10 +605,13 @@ def sodurax_workload(args) -> int:
 # width, heads, window and experts (its closest relative: windowed attention with biased projections and routed
 # experts chosen by groups).
 MEMIPEL_SIZES = {
-    "w1024": dict(width=1024, heads=16, kv=4, dim=64, q_rank=384, kv_rank=128, lt_heads=16, lt_dim=64, experts=16, ff=512,
-                  top=4, groups=4, keep=2, window=1024, conv=3),
-    "w2048": dict(width=2048, heads=32, kv=8, dim=64, q_rank=768, kv_rank=256, lt_heads=16, lt_dim=128, experts=32,
-                  ff=1024, top=4, groups=8, keep=4, window=2048, conv=4),
+    "w1024": dict(width=1024, heads=16, kv=4, dim=64, la_heads=16, la_dim=64, q_rank=384, kv_rank=128, lt_heads=16, lt_dim=64,
+                  experts=16, ff=512, top=4, groups=4, keep=2, window=1024, conv=3),
+    "w2048": dict(width=2048, heads=32, kv=8, dim=64, la_heads=16, la_dim=128, q_rank=768, kv_rank=128, lt_heads=16, lt_dim=128,
+                  experts=32, ff=1024, top=4, groups=8, keep=4, window=2048, conv=4),
+    # a latent wider than the tensor-core attention kernels take (the FP32-arithmetic kernel runs it)
+    "w2048r256": dict(width=2048, heads=32, kv=8, dim=64, la_heads=32, la_dim=64, q_rank=768, kv_rank=256, lt_heads=16,
+                      lt_dim=128, experts=32, ff=1024, top=4, groups=8, keep=4, window=2048, conv=4),
 }
 MEMIPEL_LAYERS = 6
 
@@ -621,8 +624,8 @@ def memipel_configs(z):
     lightning = {"type": "lightning", "mixer": {"heads": H, "dim": z["lt_dim"], "vdim": z["lt_dim"],
                                                 "decay": [1.0 - 2.0 ** -(1 + 8 * h / H) for h in range(H)]}, "mlp": moe}
     latent = {"type": "latent_attention",
-              "mixer": {"heads": z["heads"], "dim": z["dim"], "vdim": z["dim"], "q_rank": z["q_rank"], "kv_rank": z["kv_rank"],
-                        "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]}}, "mlp": moe}
+              "mixer": {"heads": z["la_heads"], "dim": z["la_dim"], "vdim": z["la_dim"], "q_rank": z["q_rank"],
+                        "kv_rank": z["kv_rank"], "scale": z["la_dim"] ** -0.5, "mask": {"size": z["window"]}}, "mlp": moe}
     attention = {"type": "attention",
                  "mixer": {"heads": z["heads"], "kv_heads": z["kv"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
                            "conv": z["conv"], "v_mix": True, "mask": {"size": z["window"]}}, "mlp": moe}
@@ -646,7 +649,7 @@ def memipel_workload(args) -> int:
     sampler.start()
     out = {}
     for name, z in MEMIPEL_SIZES.items():
-        if args.sizes and name not in args.sizes.split(","):
+        if (args.sizes and name not in args.sizes.split(",")) or (not args.sizes and name == "w2048r256"):
             continue
         row = {}
         for which, cfg in zip(("memipel", "sodurax"), memipel_configs(z)):
@@ -661,14 +664,14 @@ def memipel_workload(args) -> int:
             touched = min(z["experts"], args.batch * z["top"])
             keys, keys_pre = min(kv_mid, z["window"]), min(T / 2, z["window"])
             if which == "memipel":
-                LH, LD, Rq, R = z["lt_heads"], z["lt_dim"], z["q_rank"], z["kv_rank"]
+                LH, LD, Rq, R, LaH, LaD = z["lt_heads"], z["lt_dim"], z["q_rank"], z["kv_rank"], z["la_heads"], z["la_dim"]
                 moe_dec = touched * 3 * z["ff"] * W + z["experts"] * W + 3 * z["ff"] * W
                 moe_tok = (z["top"] + 1) * 3 * z["ff"] * W + z["experts"] * W
                 mix_w = {"lightning": 4 * LH * LD * W + LH * LD * W,
-                         "latent": (Rq + R) * W + H * D * Rq + 2 * H * D * R + H * D * W,
+                         "latent": (Rq + R) * W + LaH * LaD * Rq + 2 * LaH * LaD * R + LaH * LaD * W,
                          "attention": W * (H * D + 2 * G * D) + H * D * W}
                 cache_dec = {"lightning": 2 * LH * LD * LD * 4, "latent": keys * R * 2, "attention": keys * 2 * G * D * 2}
-                attn_pre = {"lightning": 2 * LH * LD * LD, "latent": 2 * keys_pre * H * R, "attention": 2 * keys_pre * H * D}
+                attn_pre = {"lightning": 2 * LH * LD * LD, "latent": 2 * keys_pre * LaH * R, "attention": 2 * keys_pre * H * D}
                 order = ["lightning", "latent", "attention"] * 2
                 ffs_dec = [2 * z["top"] * z["ff"] * W] + [moe_dec] * 5
                 ffs_tok = [2 * z["top"] * z["ff"] * W] + [moe_tok] * 5

@@ -9,8 +9,8 @@
 //
 // One kernel serves prompt portions and single tokens.  The columns of S are independent, so a block owns
 // (segment, head, a group of value columns) and walks the segment's tokens in order; a column's D state values
-// are spread over L lanes (L a power of two, D / L <= 16 values in registers per lane), the read-out is summed
-// over those lanes by shuffles.  The tokens' q, k and v are staged through shared memory a tile at a time.
+// are spread over L lanes (L a power of two, 16 values in registers per lane, zeros behind D), the read-out is
+// summed over those lanes by shuffles.  The tokens' q, k and v are staged through shared memory a tile at a time.
 // The state is stored [slot][head][value column][feature] so that a lane's values are contiguous.
 //
 // gated_rmsnorm: y = (o / sqrt(mean(o^2) + eps)) * w * sigmoid(g) over the concatenated heads of a token, the
@@ -29,50 +29,59 @@ __global__ void __launch_bounds__(LT_THREADS)
 lightning_kernel(const T* __restrict__ proj, int row_stride, float* __restrict__ state, long long slot_stride,
                  const float* __restrict__ decay, const int* __restrict__ seg_start, const int* __restrict__ slots,
                  float* __restrict__ out, int H, int D, int Dv, int tile) {
-    extern __shared__ float lt_smem[];
+    extern __shared__ __align__(16) float lt_smem[];
     constexpr int COLS = LT_THREADS / L;            // value columns of a block
+    constexpr int DP = L * LT_PER_LANE;             // features of a head, padded to whole lanes (zeros behind D)
     pdl_launch_dependents();
     pdl_wait();
     const int s = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * COLS;
-    const int col = c0 + threadIdx.x / L, part = threadIdx.x % L;
-    const int per = (D + L - 1) / L;                // features of a lane (<= LT_PER_LANE)
-    const int d0 = part * per;
+    const int cw = threadIdx.x / L, part = threadIdx.x % L;
+    const int col = c0 + cw;
+    const int d0 = part * LT_PER_LANE;              // this lane's features d0 .. d0 + 15
     const bool live = col < Dv;
     const int t0 = seg_start[s], n = seg_start[s + 1] - t0;
     const float g = decay[h];
     float* st = state + (size_t)slots[s] * slot_stride + ((size_t)h * Dv + (live ? col : 0)) * D;
     float S[LT_PER_LANE];
 #pragma unroll
-    for (int i = 0; i < LT_PER_LANE; ++i) S[i] = (live && i < per && d0 + i < D) ? st[d0 + i] : 0.f;
-    float* sq = lt_smem;                            // [tile][D]
-    float* sk = sq + (size_t)tile * D;              // [tile][D]
-    float* sv = sk + (size_t)tile * D;              // [tile][COLS]
+    for (int i = 0; i < LT_PER_LANE; ++i) S[i] = (live && d0 + i < D) ? st[d0 + i] : 0.f;
+    float* sq = lt_smem;                            // [tile][DP]
+    float* sk = sq + (size_t)tile * DP;             // [tile][DP]
+    float* sv = sk + (size_t)tile * DP;             // [tile][COLS]
     const int qo = h * D, ko = H * D + h * D, vo = 2 * H * D + h * Dv;
     for (int base = 0; base < n; base += tile) {
         const int m = min(tile, n - base);
         __syncthreads();
-        for (int j = threadIdx.x; j < m * D; j += LT_THREADS) {
-            const T* row = proj + (size_t)(t0 + base + j / D) * row_stride;
-            sq[j] = silu_f(to_f32(row[qo + j % D]));
-            sk[j] = silu_f(to_f32(row[ko + j % D]));
+        for (int j = threadIdx.x; j < m * DP; j += LT_THREADS) {
+            const int d = j % DP;
+            const T* row = proj + (size_t)(t0 + base + j / DP) * row_stride;
+            sq[j] = d < D ? silu_f(to_f32(row[qo + d])) : 0.f;
+            sk[j] = d < D ? silu_f(to_f32(row[ko + d])) : 0.f;
         }
         for (int j = threadIdx.x; j < m * COLS; j += LT_THREADS) {
             const int c = c0 + j % COLS;
             sv[j] = c < Dv ? silu_f(to_f32(proj[(size_t)(t0 + base + j / COLS) * row_stride + vo + c])) : 0.f;
         }
         __syncthreads();
+#pragma unroll 2
         for (int i = 0; i < m; ++i) {
-            const float v = sv[i * COLS + threadIdx.x / L];
-            const float* qi = sq + (size_t)i * D + d0;
-            const float* ki = sk + (size_t)i * D + d0;
-            float o = 0.f;
+            const float v = sv[i * COLS + cw];
+            const float4* q4 = reinterpret_cast<const float4*>(sq + (size_t)i * DP + d0);
+            const float4* k4 = reinterpret_cast<const float4*>(sk + (size_t)i * DP + d0);
+            float o0 = 0.f, o1 = 0.f;
 #pragma unroll
-            for (int r = 0; r < LT_PER_LANE; ++r) {
-                if (r < per && d0 + r < D) {
-                    S[r] = fmaf(g, S[r], ki[r] * v);
-                    o = fmaf(S[r], qi[r], o);
-                }
+            for (int r = 0; r < LT_PER_LANE / 4; ++r) {
+                const float4 kk = k4[r], qq = q4[r];
+                S[4 * r] = fmaf(g, S[4 * r], kk.x * v);
+                S[4 * r + 1] = fmaf(g, S[4 * r + 1], kk.y * v);
+                S[4 * r + 2] = fmaf(g, S[4 * r + 2], kk.z * v);
+                S[4 * r + 3] = fmaf(g, S[4 * r + 3], kk.w * v);
+                o0 = fmaf(S[4 * r], qq.x, o0);
+                o1 = fmaf(S[4 * r + 1], qq.y, o1);
+                o0 = fmaf(S[4 * r + 2], qq.z, o0);
+                o1 = fmaf(S[4 * r + 3], qq.w, o1);
             }
+            float o = o0 + o1;
 #pragma unroll
             for (int x = L / 2; x > 0; x >>= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
             if (part == 0 && live) out[(size_t)(t0 + base + i) * H * Dv + (size_t)h * Dv + col] = o;
@@ -81,7 +90,125 @@ lightning_kernel(const T* __restrict__ proj, int row_stride, float* __restrict__
     if (live) {
 #pragma unroll
         for (int i = 0; i < LT_PER_LANE; ++i)
-            if (i < per && d0 + i < D) st[d0 + i] = S[i];
+            if (d0 + i < D) st[d0 + i] = S[i];
+    }
+}
+
+// The same walk for bfloat16 rows whose sizes allow 16-byte reads (D, Dv, the row stride and the columns of a block
+// in multiples of 8, at most 256 features): the NEXT tile's q, k and v are requested into registers before the
+// current tile's tokens are walked, so that the walk hides the latency of the reads (one long prompt gives a block
+// per (head, column group) and nothing else on an SM to hide it).
+#define LT_FAST_ELEMS 4096        // tile * DP at most: q and k chunks of a tile are up to 4 + 4 reads of 16 bytes per thread
+#define LT_FAST_TILE_MAX 64       // tokens of a tile at most (narrow heads)
+#define LT_SLICE 20               // floats between the slices of two lanes in shared memory (16 used)
+
+__device__ __forceinline__ void silu8_to_smem(const uint4& u, float* dst) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        dst[2 * i] = silu_f(__low2float(p[i]));
+        dst[2 * i + 1] = silu_f(__high2float(p[i]));
+    }
+}
+
+template <int L>
+__global__ void __launch_bounds__(LT_THREADS)
+lightning_fast_kernel(const bf16* __restrict__ proj, int row_stride, float* __restrict__ state, long long slot_stride,
+                      const float* __restrict__ decay, const int* __restrict__ seg_start, const int* __restrict__ slots,
+                      float* __restrict__ out, int H, int D, int Dv) {
+    extern __shared__ __align__(16) float lt_smem[];
+    constexpr int COLS = LT_THREADS / L;
+    constexpr int DP = L * LT_PER_LANE;
+    constexpr int TILE = LT_FAST_ELEMS / DP < LT_FAST_TILE_MAX ? LT_FAST_ELEMS / DP : LT_FAST_TILE_MAX;
+    constexpr int QK_CHUNKS = TILE * DP / 8;                  // 16-byte pieces of a tile's q (and of its k)
+    constexpr int NPQ = QK_CHUNKS / LT_THREADS;               // per thread: 4
+    constexpr int V_CHUNKS = TILE * COLS / 8;
+    constexpr int NPV = (V_CHUNKS + LT_THREADS - 1) / LT_THREADS;
+    // a lane's 16 features lie LT_SLICE floats apart in shared memory: the lanes of a column then read their
+    // 16-byte pieces from different banks (a stride of 16 floats would put every other lane on the same ones)
+    constexpr int ROW = L * LT_SLICE;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int s = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * COLS;
+    const int cw = threadIdx.x / L, part = threadIdx.x % L;
+    const int col = c0 + cw;
+    const int d0 = part * LT_PER_LANE;
+    const bool live = col < Dv;
+    const int t0 = seg_start[s], n = seg_start[s + 1] - t0;
+    const float g = decay[h];
+    float* st = state + (size_t)slots[s] * slot_stride + ((size_t)h * Dv + (live ? col : 0)) * D;
+    float S[LT_PER_LANE];
+#pragma unroll
+    for (int i = 0; i < LT_PER_LANE; ++i) S[i] = (live && d0 + i < D) ? st[d0 + i] : 0.f;
+    float* sq = lt_smem;
+    float* sk = sq + TILE * ROW;
+    float* sv = sk + TILE * ROW;
+    const int qo = h * D, ko = H * D + h * D, vo = 2 * H * D + h * Dv;
+    uint4 pq[NPQ], pk[NPQ], pv[NPV];
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    auto request = [&](int base) {                            // the tile that starts at token `base` of the segment
+        const int m = min(TILE, n - base);
+#pragma unroll
+        for (int p = 0; p < NPQ; ++p) {
+            const int c = threadIdx.x + p * LT_THREADS, tok = c / (DP / 8), d = (c % (DP / 8)) * 8;
+            const bool on = tok < m && d < D;
+            const bf16* row = proj + (size_t)(t0 + base + (on ? tok : 0)) * row_stride;
+            pq[p] = on ? *reinterpret_cast<const uint4*>(row + qo + d) : zero;
+            pk[p] = on ? *reinterpret_cast<const uint4*>(row + ko + d) : zero;
+        }
+#pragma unroll
+        for (int p = 0; p < NPV; ++p) {
+            const int c = threadIdx.x + p * LT_THREADS, tok = c / (COLS / 8), cc = c0 + (c % (COLS / 8)) * 8;
+            const bool on = c < V_CHUNKS && tok < m && cc < Dv;
+            pv[p] = on ? *reinterpret_cast<const uint4*>(proj + (size_t)(t0 + base + tok) * row_stride + vo + cc) : zero;
+        }
+    };
+    if (n > 0) request(0);
+    for (int base = 0; base < n; base += TILE) {
+        const int m = min(TILE, n - base);
+        __syncthreads();                                      // the walk of the tile before is over
+#pragma unroll
+        for (int p = 0; p < NPQ; ++p) {                       // silu(0) = 0: padding stays zero
+            const int c = threadIdx.x + p * LT_THREADS, tok = c / (DP / 8), d = (c % (DP / 8)) * 8;
+            const int at = tok * ROW + (d / LT_PER_LANE) * LT_SLICE + d % LT_PER_LANE;
+            silu8_to_smem(pq[p], sq + at);
+            silu8_to_smem(pk[p], sk + at);
+        }
+#pragma unroll
+        for (int p = 0; p < NPV; ++p) {
+            const int c = threadIdx.x + p * LT_THREADS;
+            if (c < V_CHUNKS) silu8_to_smem(pv[p], sv + (size_t)c * 8);
+        }
+        __syncthreads();
+        if (base + TILE < n) request(base + TILE);            // in flight while this tile is walked
+#pragma unroll 2
+        for (int i = 0; i < m; ++i) {
+            const float v = sv[i * COLS + cw];
+            const float4* q4 = reinterpret_cast<const float4*>(sq + i * ROW + part * LT_SLICE);
+            const float4* k4 = reinterpret_cast<const float4*>(sk + i * ROW + part * LT_SLICE);
+            float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+            for (int r = 0; r < LT_PER_LANE / 4; ++r) {
+                const float4 kk = k4[r], qq = q4[r];
+                S[4 * r] = fmaf(g, S[4 * r], kk.x * v);
+                S[4 * r + 1] = fmaf(g, S[4 * r + 1], kk.y * v);
+                S[4 * r + 2] = fmaf(g, S[4 * r + 2], kk.z * v);
+                S[4 * r + 3] = fmaf(g, S[4 * r + 3], kk.w * v);
+                o0 = fmaf(S[4 * r], qq.x, o0);
+                o1 = fmaf(S[4 * r + 1], qq.y, o1);
+                o0 = fmaf(S[4 * r + 2], qq.z, o0);
+                o1 = fmaf(S[4 * r + 3], qq.w, o1);
+            }
+            float o = o0 + o1;
+#pragma unroll
+            for (int x = L / 2; x > 0; x >>= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
+            if (part == 0 && live) out[(size_t)(t0 + base + i) * H * Dv + (size_t)h * Dv + col] = o;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < LT_PER_LANE; ++i)
+            if (d0 + i < D) st[d0 + i] = S[i];
     }
 }
 
@@ -97,9 +224,32 @@ GESSO_API int gesso_lightning(const void* proj, int dtype, int row_stride, float
     while (L * LT_PER_LANE < D) L <<= 1;
     const int cols = LT_THREADS / L;
     if ((Dv + cols - 1) / cols > 65535) return GESSO_ERR_BAD_SIZE;
-    int tile = 16;
-    while (tile > 1 && (size_t)tile * (2 * D + cols) * sizeof(float) > 40 * 1024) tile >>= 1;
-    const size_t smem = (size_t)tile * (2 * D + cols) * sizeof(float);
+    const int dp = L * LT_PER_LANE;
+    if (dtype == GESSO_BF16 && L <= 16 && D % 8 == 0 && Dv % 8 == 0 && row_stride % 8 == 0 && ((size_t)proj & 15) == 0) {
+        const int ftile = LT_FAST_ELEMS / dp < LT_FAST_TILE_MAX ? LT_FAST_ELEMS / dp : LT_FAST_TILE_MAX;
+        const size_t fsmem = (size_t)ftile * (2 * L * LT_SLICE + cols) * sizeof(float);
+        const dim3 fgrid(n_segs, H, (Dv + cols - 1) / cols);
+#define FGO(LL)                                                                                                    \
+    static bool configured##LL = false;   /* once per instantiation, outside any stream capture */                 \
+    if (!configured##LL) {                                                                                         \
+        cudaFuncSetAttribute(lightning_fast_kernel<LL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);   \
+        configured##LL = true;                                                                                     \
+    }                                                                                                              \
+    launch_pdl(lightning_fast_kernel<LL>, fgrid, dim3(LT_THREADS), fsmem, stream, (const bf16*)proj, row_stride,   \
+               state, slot_stride, decay, seg_start, slots, out, H, D, Dv)
+        switch (L) {
+            case 1: { FGO(1); break; }
+            case 2: { FGO(2); break; }
+            case 4: { FGO(4); break; }
+            case 8: { FGO(8); break; }
+            default: { FGO(16); break; }
+        }
+#undef FGO
+        return launch_status();
+    }
+    int tile = 32;
+    while (tile > 1 && (size_t)tile * (2 * dp + cols) * sizeof(float) > 44 * 1024) tile >>= 1;
+    const size_t smem = (size_t)tile * (2 * dp + cols) * sizeof(float);
     const dim3 grid(n_segs, H, (Dv + cols - 1) / cols);
 #define GO(T, LL)                                                                                                  \
     launch_pdl(lightning_kernel<T, LL>, grid, dim3(LT_THREADS), smem, stream, (const T*)proj, row_stride, state,   \
