@@ -111,10 +111,19 @@ def _check() -> int:
              "mlp": {"kind": "moe", "expert": {"ff": 64}, "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}}}}
     sodurax = {"architecture": "Sodurax", "vocab": 320, "width": 128, "norm": {"eps": 1e-6},
                "layers": [layer, layer, dict(layer, weights_of=0)]}
+    moe = {"kind": "moe", "expert": {"ff": 48, "limit": 3.0}, "router": {"experts": 6, "top": 2, "groups": {"count": 3, "keep": 2}},
+           "shared": {"ff": 32, "limit": 2.0}}
+    memipel = {"architecture": "Memipel", "vocab": 320, "width": 128, "norm": {"eps": 1e-6}, "layers": [
+        {"type": "lightning", "mixer": {"heads": 2, "dim": 32, "vdim": 48, "decay": [0.9, 0.99]}, "mlp": {"kind": "dense", "ff": 192}},
+        {"type": "latent_attention", "mixer": {"heads": 4, "dim": 32, "vdim": 32, "q_rank": 48, "kv_rank": 64, "scale": 0.18,
+                                               "mask": {"size": 12}}, "mlp": moe},
+        {"type": "attention", "mixer": {"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 32, "scale": 0.18, "conv": 3, "v_mix": True,
+                                        "mask": {"size": 10}}, "mlp": moe}]}
     prompts = [[5, 17, 3, 250, 9, 77, 41], [1] * 19, [300]]
     # a mixture of experts may choose another expert on a close call in bfloat16, which moves the logits by more
     # than rounding: its decoding is held to a whole run in float32 only
-    for cfg, runs in ((lfm2, (("float32", 1e-4), ("bfloat16", 0.0625))), (sodurax, (("float32", 1e-4), ("bfloat16", None)))):
+    for cfg, runs in ((lfm2, (("float32", 1e-4), ("bfloat16", 0.0625))), (sodurax, (("float32", 1e-4), ("bfloat16", None))),
+                      (memipel, (("float32", 1e-4), ("bfloat16", None)))):
         with tempfile.TemporaryDirectory() as d:
             write_random_model(d, cfg, 0, style="fan_in")
             for dtype, slack in runs:

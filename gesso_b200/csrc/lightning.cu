@@ -97,8 +97,10 @@ lightning_kernel(const T* __restrict__ proj, int row_stride, float* __restrict__
 // The same walk for bfloat16 rows whose sizes allow 16-byte reads (D, Dv, the row stride and the columns of a block
 // in multiples of 8, at most 256 features): the NEXT tile's q, k and v are requested into registers before the
 // current tile's tokens are walked, so that the walk hides the latency of the reads (one long prompt gives a block
-// per (head, column group) and nothing else on an SM to hide it).
-#define LT_FAST_ELEMS 4096        // tile * DP at most: q and k chunks of a tile are up to 4 + 4 reads of 16 bytes per thread
+// per (head, column group) and nothing else on an SM to hide it).  Blocks of 32 or 64 threads (more blocks, fewer
+// columns each) were measured and are slower: 766 against 434 us for 2,048 tokens of 16 heads of 64, since a
+// block's four warps hide each other's shared-memory and shuffle latencies.
+#define LT_FAST_ELEMS_PER_THREAD 32   // tile * DP / threads at most: q and k chunks of a tile are up to 4 + 4 reads of 16 bytes per thread
 #define LT_FAST_TILE_MAX 64       // tokens of a tile at most (narrow heads)
 #define LT_SLICE 20               // floats between the slices of two lanes in shared memory (16 used)
 
@@ -111,19 +113,20 @@ __device__ __forceinline__ void silu8_to_smem(const uint4& u, float* dst) {
     }
 }
 
-template <int L>
-__global__ void __launch_bounds__(LT_THREADS)
+template <int L, int THREADS>
+__global__ void __launch_bounds__(THREADS)
 lightning_fast_kernel(const bf16* __restrict__ proj, int row_stride, float* __restrict__ state, long long slot_stride,
                       const float* __restrict__ decay, const int* __restrict__ seg_start, const int* __restrict__ slots,
                       float* __restrict__ out, int H, int D, int Dv) {
     extern __shared__ __align__(16) float lt_smem[];
-    constexpr int COLS = LT_THREADS / L;
+    constexpr int COLS = THREADS / L;
     constexpr int DP = L * LT_PER_LANE;
-    constexpr int TILE = LT_FAST_ELEMS / DP < LT_FAST_TILE_MAX ? LT_FAST_ELEMS / DP : LT_FAST_TILE_MAX;
+    constexpr int ELEMS = LT_FAST_ELEMS_PER_THREAD * THREADS;
+    constexpr int TILE = ELEMS / DP < LT_FAST_TILE_MAX ? ELEMS / DP : LT_FAST_TILE_MAX;
     constexpr int QK_CHUNKS = TILE * DP / 8;                  // 16-byte pieces of a tile's q (and of its k)
-    constexpr int NPQ = QK_CHUNKS / LT_THREADS;               // per thread: 4
+    constexpr int NPQ = QK_CHUNKS / THREADS;               // per thread: 4
     constexpr int V_CHUNKS = TILE * COLS / 8;
-    constexpr int NPV = (V_CHUNKS + LT_THREADS - 1) / LT_THREADS;
+    constexpr int NPV = (V_CHUNKS + THREADS - 1) / THREADS;
     // a lane's 16 features lie LT_SLICE floats apart in shared memory: the lanes of a column then read their
     // 16-byte pieces from different banks (a stride of 16 floats would put every other lane on the same ones)
     constexpr int ROW = L * LT_SLICE;
@@ -150,7 +153,7 @@ lightning_fast_kernel(const bf16* __restrict__ proj, int row_stride, float* __re
         const int m = min(TILE, n - base);
 #pragma unroll
         for (int p = 0; p < NPQ; ++p) {
-            const int c = threadIdx.x + p * LT_THREADS, tok = c / (DP / 8), d = (c % (DP / 8)) * 8;
+            const int c = threadIdx.x + p * THREADS, tok = c / (DP / 8), d = (c % (DP / 8)) * 8;
             const bool on = tok < m && d < D;
             const bf16* row = proj + (size_t)(t0 + base + (on ? tok : 0)) * row_stride;
             pq[p] = on ? *reinterpret_cast<const uint4*>(row + qo + d) : zero;
@@ -158,7 +161,7 @@ lightning_fast_kernel(const bf16* __restrict__ proj, int row_stride, float* __re
         }
 #pragma unroll
         for (int p = 0; p < NPV; ++p) {
-            const int c = threadIdx.x + p * LT_THREADS, tok = c / (COLS / 8), cc = c0 + (c % (COLS / 8)) * 8;
+            const int c = threadIdx.x + p * THREADS, tok = c / (COLS / 8), cc = c0 + (c % (COLS / 8)) * 8;
             const bool on = c < V_CHUNKS && tok < m && cc < Dv;
             pv[p] = on ? *reinterpret_cast<const uint4*>(proj + (size_t)(t0 + base + tok) * row_stride + vo + cc) : zero;
         }
@@ -169,14 +172,14 @@ lightning_fast_kernel(const bf16* __restrict__ proj, int row_stride, float* __re
         __syncthreads();                                      // the walk of the tile before is over
 #pragma unroll
         for (int p = 0; p < NPQ; ++p) {                       // silu(0) = 0: padding stays zero
-            const int c = threadIdx.x + p * LT_THREADS, tok = c / (DP / 8), d = (c % (DP / 8)) * 8;
+            const int c = threadIdx.x + p * THREADS, tok = c / (DP / 8), d = (c % (DP / 8)) * 8;
             const int at = tok * ROW + (d / LT_PER_LANE) * LT_SLICE + d % LT_PER_LANE;
             silu8_to_smem(pq[p], sq + at);
             silu8_to_smem(pk[p], sk + at);
         }
 #pragma unroll
         for (int p = 0; p < NPV; ++p) {
-            const int c = threadIdx.x + p * LT_THREADS;
+            const int c = threadIdx.x + p * THREADS;
             if (c < V_CHUNKS) silu8_to_smem(pv[p], sv + (size_t)c * 8);
         }
         __syncthreads();
@@ -226,23 +229,29 @@ GESSO_API int gesso_lightning(const void* proj, int dtype, int row_stride, float
     if ((Dv + cols - 1) / cols > 65535) return GESSO_ERR_BAD_SIZE;
     const int dp = L * LT_PER_LANE;
     if (dtype == GESSO_BF16 && L <= 16 && D % 8 == 0 && Dv % 8 == 0 && row_stride % 8 == 0 && ((size_t)proj & 15) == 0) {
-        const int ftile = LT_FAST_ELEMS / dp < LT_FAST_TILE_MAX ? LT_FAST_ELEMS / dp : LT_FAST_TILE_MAX;
-        const size_t fsmem = (size_t)ftile * (2 * L * LT_SLICE + cols) * sizeof(float);
-        const dim3 fgrid(n_segs, H, (Dv + cols - 1) / cols);
-#define FGO(LL)                                                                                                    \
-    static bool configured##LL = false;   /* once per instantiation, outside any stream capture */                 \
-    if (!configured##LL) {                                                                                         \
-        cudaFuncSetAttribute(lightning_fast_kernel<LL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);   \
-        configured##LL = true;                                                                                     \
-    }                                                                                                              \
-    launch_pdl(lightning_fast_kernel<LL>, fgrid, dim3(LT_THREADS), fsmem, stream, (const bf16*)proj, row_stride,   \
-               state, slot_stride, decay, seg_start, slots, out, H, D, Dv)
+        const int threads = LT_THREADS;
+        const int fcols = threads / L;
+        const int elems = LT_FAST_ELEMS_PER_THREAD * threads;
+        const int ftile = elems / dp < LT_FAST_TILE_MAX ? elems / dp : LT_FAST_TILE_MAX;
+        const size_t fsmem = (size_t)ftile * (2 * L * LT_SLICE + fcols) * sizeof(float);
+        const dim3 fgrid(n_segs, H, (Dv + fcols - 1) / fcols);
+#define FGO(LL, TH)                                                                                                \
+    do {                                                                                                           \
+        static bool configured = false;   /* once per instantiation, outside any stream capture */                 \
+        if (!configured) {                                                                                         \
+            cudaFuncSetAttribute(lightning_fast_kernel<LL, TH>, cudaFuncAttributeMaxDynamicSharedMemorySize,       \
+                                 64 * 1024);                                                                       \
+            configured = true;                                                                                     \
+        }                                                                                                          \
+        launch_pdl(lightning_fast_kernel<LL, TH>, fgrid, dim3(TH), fsmem, stream, (const bf16*)proj, row_stride,   \
+                   state, slot_stride, decay, seg_start, slots, out, H, D, Dv);                                    \
+    } while (0)
         switch (L) {
-            case 1: { FGO(1); break; }
-            case 2: { FGO(2); break; }
-            case 4: { FGO(4); break; }
-            case 8: { FGO(8); break; }
-            default: { FGO(16); break; }
+            case 1: FGO(1, 128); break;
+            case 2: FGO(2, 128); break;
+            case 4: FGO(4, 128); break;
+            case 8: FGO(8, 128); break;
+            default: FGO(16, 128); break;
         }
 #undef FGO
         return launch_status();
