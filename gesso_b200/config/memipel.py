@@ -119,9 +119,7 @@ class MemipelAttention:
         kv = _int(m, "kv_heads", what, default=heads)
         if heads % kv != 0:
             raise invalid(f"Memipel config: {what}: {heads} heads are not a multiple of {kv} kv_heads")
-        dim = _int(m, "dim", what, 2)
-        if dim % 2 != 0:
-            raise invalid(f"Memipel config: {what}.dim {dim} must be even")
+        dim = _int(m, "dim", what)
         conv = None if m.get("conv") is None else _int(m, "conv", what)
         v_mix = m.get("v_mix", False)
         if not isinstance(v_mix, bool):

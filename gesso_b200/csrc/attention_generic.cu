@@ -1,4 +1,4 @@
-// Paged causal attention for any head size, in float32 arithmetic (CUDA cores).
+// Paged causal attention for any head size up to 512, in float32 arithmetic (CUDA cores).
 //
 // This is the kernel of the true 32-bit path, and the bfloat16 path uses it for head sizes its
 // tensor-core kernels do not take.  One warp per (token, query head).  A query at absolute
@@ -116,6 +116,7 @@ static int launch_generic(const void* q, const void* k_pages, const void* v_page
     else if (wide <= 64) GO(64);
     else if (wide <= 128) GO(128);
     else if (wide <= 256) GO(256);
+    else if (wide <= 512) GO(512);
     else return GESSO_ERR_BAD_SIZE;
 #undef GO
     return launch_status();

@@ -308,7 +308,8 @@ GESSO_API int gesso_qk_norm_rope_store(const void* qkv, int dtype, const float* 
                                        int* status, const float* bias, int row_stride, int vd,
                                        cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (hd <= 0 || (hd & 1) || nh <= 0 || nkv <= 0 || page_size <= 0) return GESSO_ERR_BAD_SIZE;
+    // an odd head size only where heads are neither normed nor rotated (both work on pairs of features)
+    if (hd <= 0 || ((hd & 1) && (q_w || k_w || cos_t)) || nh <= 0 || nkv <= 0 || page_size <= 0) return GESSO_ERR_BAD_SIZE;
     if (vd <= 0) vd = hd;                                      // values as wide as keys
     if (row_stride <= 0) row_stride = write_kv ? (nh + nkv) * hd + nkv * vd : nh * hd;
     if (row_stride < (write_kv ? (nh + nkv) * hd + nkv * vd : nh * hd)) return GESSO_ERR_BAD_SIZE;

@@ -87,8 +87,9 @@ class GQAttention(Mixer):
             raise invalid("attention: keep_first must be >= 0")
         if self.nh < 1 or self.nkv < 1 or self.nh % self.nkv != 0:
             raise invalid(f"attention: {self.nh} heads are not a multiple of {self.nkv} kv heads")
-        if self.hd < 2 or self.hd % 2 != 0 or self.hd > 256:
-            raise invalid(f"attention: head_dim {self.hd} must be even and at most 256")
+        rotates_or_norms = spec["position"].kind != "none" or self.eps is not None
+        if self.hd < 1 or self.hd > 256 or (rotates_or_norms and self.hd % 2 != 0):
+            raise invalid(f"attention: head_dim {self.hd} must be at most 256, and even where heads are rotated or normed")
         if self.window is not None and int(self.window) < 1:
             raise invalid("attention: window must be >= 1")
         self.position = build_position(spec["position"])

@@ -58,8 +58,8 @@ class LatentAttention(Mixer):
         self.eps = float(spec["norm_eps"])
         if min(self.nh, self.hd, self.vd, self.q_rank, self.kv_rank) < 1:
             raise invalid("latent attention: sizes must be positive")
-        if self.kv_rank > 256:
-            raise invalid(f"latent attention: kv_rank {self.kv_rank} is above 256, the most the attention kernel takes")
+        if self.kv_rank > 512:
+            raise invalid(f"latent attention: kv_rank {self.kv_rank} is above 512, the most the attention kernel takes")
         if self.window is not None and int(self.window) < 1:
             raise invalid("latent attention: window must be >= 1")
         self.mirror = False       # decided when the weights are bound (the run type decides)

@@ -46,11 +46,11 @@ MMP_A = {"architecture": "Memipel", "vocab": 131, "width": 64, "norm": {"eps": 1
     lightning(2, 16, 24, [0.9, 0.5], None),
 ]}
 
-# sizes that are no multiples of 8 or powers of two: values wider than keys, a convolution of four taps, a window
+# sizes that are no multiples of 8 or powers of two: an odd head size, values wider than keys, a convolution of four taps, a window
 # longer than most prompts, latent attention over all keys with one head, decays of exactly one and near zero,
 # experts without groups and without a shared expert (every expert chosen: top = experts), expert width 20.
 MMP_B = {"architecture": "Memipel", "vocab": 257, "width": 96, "norm": {"eps": 1e-6}, "layers": [
-    attention(3, 3, 8, 40, 0.4, 4, 130, False, _moe(20, 0.8, 4, 4)),
+    attention(3, 3, 9, 40, 0.4, 4, 130, False, _moe(20, 0.8, 4, 4)),
     latent(1, 48, 48, 8, 80, 0.15, None, _dense(72)),
     lightning(3, 40, 8, [1.0, 0.05, 0.97], _moe(20, 2.5, 5, 2, (5, 3))),
 ]}
@@ -63,6 +63,13 @@ MMP_C = {"architecture": "Memipel", "vocab": 300, "width": 128, "norm": {"eps": 
     lightning(2, 64, 64, [0.999, 0.8], _moe(32, 2.0, 16, 3, (8, 5), (64, 1.2))),
     attention(4, 2, 64, 64, 0.125, 1, 48, True, _moe(48, 1.0, 8, 1, (4, 1))),
 ]}
+
+# stacks of one kind of mixer only: no pages at all (every layer keeps a state), no state at all (every layer keeps
+# pages), a latent wider than 256
+MMP_ONLY_STATE = {"architecture": "Memipel", "vocab": 90, "width": 48, "norm": {"eps": 1e-6}, "layers": [
+    lightning(3, 8, 16, [0.9, 0.99, 0.5], _dense(32)), lightning(1, 24, 8, [0.95], None)]}
+MMP_ONLY_PAGES = {"architecture": "Memipel", "vocab": 90, "width": 48, "norm": {"eps": 1e-6}, "layers": [
+    latent(2, 8, 8, 16, 272, 0.3, 25, None), latent(5, 16, 24, 8, 24, 0.2, None, _dense(64))]}
 
 # name -> (config, seed)
 MMP = {"a": (MMP_A, 21), "b": (MMP_B, 22), "c": (MMP_C, 23)}

@@ -661,6 +661,26 @@ def test_random_configuration_replays_like_plain(seed, tmp_path):
         del model
 
 
+@pytest.mark.parametrize("which", ["MMP_ONLY_STATE", "MMP_ONLY_PAGES"])
+def test_stacks_of_one_kind_of_cache(which, tmp_path):
+    """A model without any pages and one without any state go through the same engine, in both run types."""
+    import gesso_b200
+    cfg = getattr(cm, which)
+    d = str(tmp_path / "model")
+    pm.write_model(d, cfg, 4)
+    plain_model = pm.PlainMemipel.from_dir(d)
+    reqs = tt.make_requests(cfg["vocab"], [33, 1, 70, 18], seed=8)
+    ref = [plain_model.logits(t).numpy() for t in reqs]
+    for dtype in ("float32", "bfloat16"):
+        model = gesso_b200.load(d, dtype=dtype, max_positions=256)
+        for name, make in SCHEDULES.items():
+            tb, max_tokens = make(reqs)
+            out = str(tmp_path / f"{dtype}_{name}")
+            tt.run_in_process(model, tb, max_tokens, out)
+            compare(tt.read_rows(tb, out, cfg["vocab"]), ref, TOL[dtype], f"{which} {name} {dtype}")
+        del model
+
+
 def test_trace_program_on_a_model_folder(mmp_dirs, plain, tmp_path):
     reqs, ref = plain("b")
     tb, max_tokens = tt.trace_mixed(reqs, seed=2)
