@@ -43,6 +43,8 @@ _SIGNATURES = {
     "gesso_latent_norm_store": [P, I, I, P, P, F, P, I, P, P, P, I, I, P, I, P, I, P, P],
     "gesso_headwise_linear": [P, I, P, I, P, I, I, I, I, I, P],
     "gesso_lightning": [P, I, I, P, LL, P, P, P, P, I, I, I, I, I, P],
+    "gesso_lightning_chunked": [P, I, I, P, LL, P, P, P, P, P, I, P, P, I, I, I, I, I, P],
+    "gesso_lightning_chunked_takes": [I, I],
     "gesso_gated_rmsnorm": [P, P, F, P, I, P, I, I, I, P],
     "gesso_skinny_gemm_takes": [I, I, I],
     "gesso_skinny_gemm": [P, P, P, F, P, P, P, I, I, I, I, P, LL, P],

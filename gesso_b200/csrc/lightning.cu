@@ -319,3 +319,275 @@ GESSO_API int gesso_gated_rmsnorm(const float* o, const float* w, float eps, con
         return GESSO_ERR_BAD_DTYPE;
     return launch_status();
 }
+
+// ---- prompt portions by chunks ------------------------------------------------------------------------------------
+// The recurrence over a long portion, cut into the step's 64-token query tiles (a tile never crosses a request), so
+// that the tiles run side by side instead of token after token.  With g the head's decay, a tile of m tokens that
+// starts from the state S0 gives
+//     o_t = g^(t+1) S0^T q_t + sum_{s <= t} g^(t-s) (q_t . k_s) v_s          (t = 0 .. m-1 inside the tile)
+//     S_m = g^m S0 + U,   U = sum_s g^(m-1-s) k_s v_s^T
+// Three launches: (1) every tile's U, from its own keys and values; (2) per (request, head) a walk over the request's
+// tiles that turns the workspace's U into the state each tile starts from and leaves the last state in the slot;
+// (3) every tile's outputs.  All float32 on the CUDA cores (4 x 4 register tiles over shared memory); the sums are
+// the recurrence's own terms in another order.  The workspace holds one state [Dv][D] per (tile, head).
+// A padded step repeats a tile at the end of its list; only a tile's first occurrence works.
+#define LC_CHUNK 64
+#define LC_THREADS 256
+
+__device__ __forceinline__ float pow_int(float lg, int e) { return e == 0 ? 1.f : exp2f(lg * (float)e); }
+
+// the tile's place in its request's list of tiles, or -1 for a repeated tile
+__device__ __forceinline__ bool lc_tile(const int* tile_seg, const int* tile_q0, const int* seg_start, int tile, int& seg,
+                                        int& q0, int& t0, int& m) {
+    seg = tile_seg[tile];
+    q0 = tile_q0[tile];
+    const int first = tile - q0 / LC_CHUNK;
+    if (first < 0 || tile_seg[first] != seg || tile_q0[first] != 0 || (first > 0 && tile_seg[first - 1] == seg)) return false;
+    t0 = seg_start[seg];
+    const int n = seg_start[seg + 1] - t0;
+    if (q0 >= n) return false;
+    m = min(LC_CHUNK, n - q0);
+    return true;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(LC_THREADS)
+lightning_chunk_state_kernel(const T* __restrict__ proj, int row_stride, const float* __restrict__ decay,
+                             const int* __restrict__ seg_start, const int* __restrict__ tile_seg,
+                             const int* __restrict__ tile_q0, float* __restrict__ ws, int H, int D, int Dv) {
+    extern __shared__ __align__(16) float lc_smem[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tile = blockIdx.x, h = blockIdx.y;
+    int seg, q0, t0, m;
+    if (!lc_tile(tile_seg, tile_q0, seg_start, tile, seg, q0, t0, m)) return;
+    const int DP = (D + 3) & ~3, VP = (Dv + 3) & ~3;
+    float* sk = lc_smem;                    // [LC_CHUNK][DP], rows already weighted by g^(m-1-s)
+    float* sv = sk + LC_CHUNK * DP;         // [LC_CHUNK][VP]
+    const float lg = log2f(decay[h]);
+    const int ko = H * D + h * D, vo = 2 * H * D + h * Dv;
+    for (int j = threadIdx.x; j < LC_CHUNK * DP; j += LC_THREADS) {
+        const int s = j / DP, d = j % DP;
+        sk[j] = (s < m && d < D) ? silu_f(to_f32(proj[(size_t)(t0 + q0 + s) * row_stride + ko + d])) * pow_int(lg, m - 1 - s) : 0.f;
+    }
+    for (int j = threadIdx.x; j < LC_CHUNK * VP; j += LC_THREADS) {
+        const int s = j / VP, c = j % VP;
+        sv[j] = (s < m && c < Dv) ? silu_f(to_f32(proj[(size_t)(t0 + q0 + s) * row_stride + vo + c])) : 0.f;
+    }
+    __syncthreads();
+    float* out = ws + ((size_t)tile * H + h) * Dv * D;
+    const int dg_n = DP / 4, vg_n = VP / 4;
+    for (int e = threadIdx.x; e < dg_n * vg_n; e += LC_THREADS) {
+        const int dg = e % dg_n, vg = e / dg_n;
+        float acc[4][4] = {};
+        for (int s = 0; s < m; ++s) {
+            const float4 kk = *reinterpret_cast<const float4*>(sk + s * DP + 4 * dg);
+            const float4 vv = *reinterpret_cast<const float4*>(sv + s * VP + 4 * vg);
+            const float ka[4] = {kk.x, kk.y, kk.z, kk.w}, va[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(va[a], ka[b], acc[a][b]);
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b)
+                if (4 * vg + a < Dv && 4 * dg + b < D) out[(size_t)(4 * vg + a) * D + 4 * dg + b] = acc[a][b];
+    }
+}
+
+__global__ void __launch_bounds__(LC_THREADS)
+lightning_chunk_scan_kernel(float* __restrict__ state, long long slot_stride, const float* __restrict__ decay,
+                            const int* __restrict__ seg_start, const int* __restrict__ slots,
+                            const int* __restrict__ tile_seg, const int* __restrict__ tile_q0, int n_tiles,
+                            float* __restrict__ ws, int H, int D, int Dv) {
+    __shared__ int s_first;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int seg = blockIdx.x, h = blockIdx.y;
+    if (threadIdx.x == 0) {
+        int f = -1;
+        for (int t = 0; t < n_tiles; ++t)
+            if (tile_seg[t] == seg && tile_q0[t] == 0) { f = t; break; }
+        s_first = f;
+    }
+    __syncthreads();
+    const int first = s_first;
+    const int e = blockIdx.z * LC_THREADS + threadIdx.x;
+    if (first < 0 || e >= D * Dv) return;
+    const int n = seg_start[seg + 1] - seg_start[seg];
+    const float lg = log2f(decay[h]);
+    float* st = state + (size_t)slots[seg] * slot_stride + (size_t)h * Dv * D + e;
+    float S = *st;
+    for (int c = 0; c * LC_CHUNK < n; ++c) {
+        float* u = ws + ((size_t)(first + c) * H + h) * Dv * D + e;
+        const float U = *u;
+        *u = S;                                             // the state this tile starts from
+        S = fmaf(pow_int(lg, min(LC_CHUNK, n - c * LC_CHUNK)), S, U);
+    }
+    *st = S;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(LC_THREADS)
+lightning_chunk_out_kernel(const T* __restrict__ proj, int row_stride, const float* __restrict__ decay,
+                           const int* __restrict__ seg_start, const int* __restrict__ tile_seg,
+                           const int* __restrict__ tile_q0, const float* __restrict__ ws, float* __restrict__ out,
+                           int H, int D, int Dv) {
+    extern __shared__ __align__(16) float lc_smem[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tile = blockIdx.x, h = blockIdx.y;
+    int seg, q0, t0, m;
+    if (!lc_tile(tile_seg, tile_q0, seg_start, tile, seg, q0, t0, m)) return;
+    const int DP = (D + 3) & ~3, VP = (Dv + 3) & ~3;
+    const int WP = DP > VP ? DP : VP;
+    float* sq = lc_smem;                        // [LC_CHUNK][DP]
+    float* sx = sq + LC_CHUNK * DP;             // [LC_CHUNK][WP]: the keys, later the values
+    float* sa = sx + LC_CHUNK * WP;             // [LC_CHUNK][LC_CHUNK + 4]: decayed scores, row t, column s
+    constexpr int AP = LC_CHUNK + 4;
+    const float lg = log2f(decay[h]);
+    const int qo = h * D, ko = H * D + h * D, vo = 2 * H * D + h * Dv;
+    for (int j = threadIdx.x; j < LC_CHUNK * DP; j += LC_THREADS) {
+        const int s = j / DP, d = j % DP;
+        const bool on = s < m && d < D;
+        const T* row = proj + (size_t)(t0 + q0 + (on ? s : 0)) * row_stride;
+        sq[j] = on ? silu_f(to_f32(row[qo + d])) : 0.f;
+        sx[s * WP + d] = on ? silu_f(to_f32(row[ko + d])) : 0.f;
+    }
+    __syncthreads();
+    // scores: 4 x 4 tiles of (t, s); above the diagonal they are zero
+    for (int e = threadIdx.x; e < (LC_CHUNK / 4) * (LC_CHUNK / 4); e += LC_THREADS) {
+        const int tg = e / (LC_CHUNK / 4), sg = e % (LC_CHUNK / 4);
+        float acc[4][4] = {};
+        if (sg <= tg) {
+            for (int d = 0; d < DP; d += 4) {
+                float4 qa[4], ka[4];
+#pragma unroll
+                for (int a = 0; a < 4; ++a) {
+                    qa[a] = *reinterpret_cast<const float4*>(sq + (4 * tg + a) * DP + d);
+                    ka[a] = *reinterpret_cast<const float4*>(sx + (4 * sg + a) * WP + d);
+                }
+#pragma unroll
+                for (int a = 0; a < 4; ++a)
+#pragma unroll
+                    for (int b = 0; b < 4; ++b)
+                        acc[a][b] += qa[a].x * ka[b].x + qa[a].y * ka[b].y + qa[a].z * ka[b].z + qa[a].w * ka[b].w;
+            }
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const int t = 4 * tg + a, s = 4 * sg + b;
+                sa[t * AP + s] = s <= t ? acc[a][b] * pow_int(lg, t - s) : 0.f;
+            }
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < LC_CHUNK * VP; j += LC_THREADS) {         // the values take the keys' place
+        const int s = j / VP, c = j % VP;
+        sx[s * WP + c] = (s < m && c < Dv) ? silu_f(to_f32(proj[(size_t)(t0 + q0 + s) * row_stride + vo + c])) : 0.f;
+    }
+    __syncthreads();
+    const float* S0 = ws + ((size_t)tile * H + h) * Dv * D;                   // [Dv][D], the state the tile starts from
+    const int vg_n = VP / 4;
+    for (int e = threadIdx.x; e < (LC_CHUNK / 4) * vg_n; e += LC_THREADS) {
+        const int tg = e / vg_n, vg = e % vg_n;
+        float acc[4][4] = {};                                               // [t][v]
+        for (int s = 0; s < 4 * tg + 4 && s < m; ++s) {
+            const float4 vv = *reinterpret_cast<const float4*>(sx + s * WP + 4 * vg);
+            const float va[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                const float w = sa[(4 * tg + a) * AP + s];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(w, va[b], acc[a][b]);
+            }
+        }
+        // the carried state: g^(t+1) * sum_d q_t[d] S0[v][d]
+        float car[4][4] = {};
+        if ((D & 3) == 0) {
+            // four features at a time: the state's rows are read as 16-byte pieces, several of them in flight
+#pragma unroll 2
+            for (int d = 0; d < D; d += 4) {
+                float4 sv4[4], qv4[4];
+#pragma unroll
+                for (int b = 0; b < 4; ++b)
+                    sv4[b] = 4 * vg + b < Dv ? __ldg(reinterpret_cast<const float4*>(S0 + (size_t)(4 * vg + b) * D + d))
+                                             : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int a = 0; a < 4; ++a) qv4[a] = *reinterpret_cast<const float4*>(sq + (4 * tg + a) * DP + d);
+#pragma unroll
+                for (int a = 0; a < 4; ++a)
+#pragma unroll
+                    for (int b = 0; b < 4; ++b)
+                        car[a][b] += qv4[a].x * sv4[b].x + qv4[a].y * sv4[b].y + qv4[a].z * sv4[b].z + qv4[a].w * sv4[b].w;
+            }
+        } else {
+            for (int d = 0; d < D; ++d) {
+                float sv4[4];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) sv4[b] = 4 * vg + b < Dv ? S0[(size_t)(4 * vg + b) * D + d] : 0.f;
+#pragma unroll
+                for (int a = 0; a < 4; ++a) {
+                    const float qv = sq[(4 * tg + a) * DP + d];
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) car[a][b] = fmaf(qv, sv4[b], car[a][b]);
+                }
+            }
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+            const int t = 4 * tg + a;
+            if (t >= m) continue;
+            const float gt = pow_int(lg, t + 1);
+#pragma unroll
+            for (int b = 0; b < 4; ++b)
+                if (4 * vg + b < Dv)
+                    out[(size_t)(t0 + q0 + t) * H * Dv + (size_t)h * Dv + 4 * vg + b] = fmaf(gt, car[a][b], acc[a][b]);
+        }
+    }
+}
+
+// Bytes of workspace for a step of n_tiles query tiles.
+GESSO_API long long gesso_lightning_chunked_workspace(int n_tiles, int H, int D, int Dv) {
+    return (long long)n_tiles * H * D * Dv * (long long)sizeof(float);
+}
+
+GESSO_API int gesso_lightning_chunked_takes(int D, int Dv) { return D >= 1 && D <= 128 && Dv >= 1 && Dv <= 128; }
+
+// The same contract as gesso_lightning for a step with prompt portions; tile_seg / tile_q0 [n_tiles]: the step's
+// 64-token query tiles; ws: gesso_lightning_chunked_workspace bytes.
+GESSO_API int gesso_lightning_chunked(const void* proj, int dtype, int row_stride, float* state, long long slot_stride,
+                                      const float* decay, const int* seg_start, const int* slots, const int* tile_seg,
+                                      const int* tile_q0, int n_tiles, float* ws, float* out, int n_tokens, int n_segs,
+                                      int H, int D, int Dv, cudaStream_t stream) {
+    if (n_tokens <= 0 || n_segs <= 0 || n_tiles <= 0) return 0;
+    if (!gesso_lightning_chunked_takes(D, Dv) || H <= 0 || H > 65535 || n_segs > 65535 || row_stride < 2 * H * D + H * Dv)
+        return GESSO_ERR_BAD_SIZE;
+    const int DP = (D + 3) & ~3, VP = (Dv + 3) & ~3, WP = DP > VP ? DP : VP;
+    const size_t smem_a = (size_t)LC_CHUNK * (DP + VP) * sizeof(float);
+    const size_t smem_c = (size_t)LC_CHUNK * (DP + WP + LC_CHUNK + 4) * sizeof(float);
+    const dim3 tiles(n_tiles, H), scan(n_segs, H, (D * Dv + LC_THREADS - 1) / LC_THREADS);
+#define GO(T)                                                                                                          \
+    do {                                                                                                               \
+        static bool configured = false;   /* once per instantiation, outside any stream capture */                     \
+        if (!configured) {                                                                                             \
+            cudaFuncSetAttribute(lightning_chunk_state_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); \
+            cudaFuncSetAttribute(lightning_chunk_out_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);   \
+            configured = true;                                                                                         \
+        }                                                                                                              \
+        launch_pdl(lightning_chunk_state_kernel<T>, tiles, dim3(LC_THREADS), smem_a, stream, (const T*)proj, row_stride, \
+                   decay, seg_start, tile_seg, tile_q0, ws, H, D, Dv);                                                 \
+        launch_pdl(lightning_chunk_scan_kernel, scan, dim3(LC_THREADS), 0, stream, state, slot_stride, decay,          \
+                   seg_start, slots, tile_seg, tile_q0, n_tiles, ws, H, D, Dv);                                        \
+        launch_pdl(lightning_chunk_out_kernel<T>, tiles, dim3(LC_THREADS), smem_c, stream, (const T*)proj, row_stride, \
+                   decay, seg_start, tile_seg, tile_q0, (const float*)ws, out, H, D, Dv);                              \
+    } while (0)
+    if (dtype == GESSO_F32) GO(float);
+    else if (dtype == GESSO_BF16) GO(bf16);
+    else return GESSO_ERR_BAD_DTYPE;
+#undef GO
+    return launch_status();
+}

@@ -610,6 +610,41 @@ def lightning_attention(proj: torch.Tensor, state: torch.Tensor, decay: torch.Te
     return out
 
 
+# Steps whose longest portion has at least this many tokens run the recurrence by 64-token chunks side by side: the
+# token-by-token walk costs 0.2 to 0.3 us a token of the longest portion, the three launches of the chunked form
+# about 80 us whatever the length (GESSO_LIGHTNING_CHUNK_MIN_TOKENS; a huge number keeps every step on the walk).
+LIGHTNING_CHUNK_MIN_TOKENS = int(os.environ.get("GESSO_LIGHTNING_CHUNK_MIN_TOKENS", "512"))
+
+
+def lightning_chunked_takes(longest_portion: int, dim: int, vdim: int) -> bool:
+    return (longest_portion >= LIGHTNING_CHUNK_MIN_TOKENS
+            and bool(_lib.library().gesso_lightning_chunked_takes(int(dim), int(vdim))))
+
+
+def lightning_attention_chunked(proj: torch.Tensor, state: torch.Tensor, decay: torch.Tensor, seg_start: torch.Tensor,
+                                slots: torch.Tensor, tile_seg: torch.Tensor, tile_q0: torch.Tensor, n_segs: int,
+                                n_heads: int, dim: int, vdim: int) -> torch.Tensor:
+    """The same result as :func:`lightning_attention` for a step with prompt portions, computed by the step's 64-token
+    query tiles side by side (``tile_seg`` / ``tile_q0``: the tiles' segments and first tokens, as the step's
+    metadata lists them): every tile's own key-value sum, a walk over each request's tiles that hands every tile the
+    state it starts from, then every tile's outputs.  float32 throughout."""
+    _need(proj.is_cuda and proj.dim() == 2 and proj.stride(1) == 1, "proj must be rows on the device")
+    H, D, Dv = int(n_heads), int(dim), int(vdim)
+    _need(proj.shape[1] >= 2 * H * D + H * Dv, "proj is narrower than q, k and v")
+    _need(state.dtype == torch.float32 and state.is_cuda and tuple(state.shape[1:]) == (H, Dv, D)
+          and state[0].is_contiguous(), "state must be [slots, heads, value size, key size] float32")
+    _cuda_contig(decay, "decay", torch.float32)
+    for name, t in (("seg_start", seg_start), ("slots", slots), ("tile_seg", tile_seg), ("tile_q0", tile_q0)):
+        _cuda_contig(t, name, torch.int32)
+    N, n_tiles = proj.shape[0], tile_seg.numel()
+    out = torch.empty((N, H * Dv), dtype=torch.float32, device=proj.device)
+    ws = torch.empty((max(n_tiles, 1) * H * Dv * D,), dtype=torch.float32, device=proj.device)
+    _lib.check(_lib.library().gesso_lightning_chunked(
+        _p(proj), _dt(proj), int(proj.stride(0)), _p(state), state.stride(0), _p(decay), _p(seg_start), _p(slots),
+        _p(tile_seg), _p(tile_q0), n_tiles, _p(ws), _p(out), N, int(n_segs), H, D, Dv, _stream()), "lightning_chunked")
+    return out
+
+
 def gated_rmsnorm(o: torch.Tensor, weight: torch.Tensor, eps: float, gate: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """``rmsnorm(o) * weight * sigmoid(gate)`` over rows of float32 ``o`` [N, W]; ``gate`` a 2-D view [N, W] of
     ``out_dtype`` with unit column stride."""

@@ -11,7 +11,9 @@ The heads of a token are then normed *together*, gated and projected::
     y_t = (o_t / sqrt(mean(o_t^2) + eps)) * w * sigmoid(W_g x_t),      out_t = W_o y_t
 
 The state S (``n_heads x head_dim x v_head_dim`` float32 numbers per request and layer) is all a request keeps; it
-is carried from token to token inside a portion and from step to step in the request's state slot.  The
+is carried from token to token inside a portion and from step to step in the request's state slot.  A step with a
+long portion computes the same sums by 64-token chunks side by side (a chunk's own key-value sum, a walk over the
+chunks that hands each its starting state, then each chunk's outputs).  The
 recurrence, the decays and the norm are float32 whatever the run type; the four projections are one fused matrix.
 
 Parameters: hidden_size, n_heads, head_dim, v_head_dim, decay (one number per head), norm_eps.  Tensors:
@@ -71,7 +73,12 @@ class LightningAttention(Mixer):
     def forward(self, x, ctx, cache):
         H, D, Dv = self.nh, self.hd, self.vd
         proj = ops.linear(x, self.w_in, out_dtype=x.dtype)
-        o = ops.lightning_attention(proj, cache.state, self.decay_dev, ctx.seg_start, cache.slots, ctx.n_segs, H, D, Dv)
+        if not ctx.decode_only and ops.lightning_chunked_takes(ctx.max_seg_len, D, Dv):
+            # long prompt portions: the step's 64-token tiles side by side instead of token after token
+            o = ops.lightning_attention_chunked(proj, cache.state, self.decay_dev, ctx.seg_start, cache.slots,
+                                                ctx.tile_seg, ctx.tile_q0, ctx.n_segs, H, D, Dv)
+        else:
+            o = ops.lightning_attention(proj, cache.state, self.decay_dev, ctx.seg_start, cache.slots, ctx.n_segs, H, D, Dv)
         g0 = 2 * H * D + H * Dv
         y = ops.gated_rmsnorm(o, self.w_norm, self.eps, proj[:, g0:g0 + H * Dv], x.dtype)
         return ops.linear(y, self.w_o, out_dtype=torch.float32), None

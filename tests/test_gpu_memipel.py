@@ -387,6 +387,33 @@ def test_lightning_recurrence_portions_and_single_tokens(H, D, Dv, dtype):
         at += n
     for r in range(2):
         check(torch.cat(got[r]), r, f"portions, request {r}")
+    if not ops.lightning_chunked_takes(10 ** 6, D, Dv):
+        return
+    # the same by 64-token tiles side by side: one portion; then uneven portions of two requests, with the tile list
+    # of a padded step (its last tile repeated)
+    def tiles(lens, extra=0):
+        ts = [(i, q0) for i, n in enumerate(lens) for q0 in range(0, n, 64)] + [(len(lens) - 1, 0)] * extra
+        return i32([t[0] for t in ts]), i32([t[1] for t in ts])
+    state[0].zero_()
+    tseg, tq0 = tiles([T])
+    check(ops.lightning_attention_chunked(rows[0], state, dd, seg_start, i32([0]), tseg, tq0, 1, H, D, Dv).double().cpu(), 0,
+          "one portion by tiles")
+    assert torch.allclose(state[0], state[2], atol=1e-4, rtol=1e-4), "the state a portion leaves, by tiles and token by token"
+    state[0].zero_()
+    state[1].zero_()
+    got, at = [[], []], 0
+    for kk, n in enumerate([130, 1, 64, 65, 40]):
+        order = [0, 1] if kk % 2 else [1, 0]
+        both = torch.cat([rows[r][at:at + n] for r in order])
+        _, start = segments([n, n])
+        tseg, tq0 = tiles([n, n], extra=kk % 3)
+        y = ops.lightning_attention_chunked(both, state, dd, start, i32([1 if r == 0 else 0 for r in order]), tseg, tq0, 2,
+                                            H, D, Dv)
+        for j, r in enumerate(order):
+            got[r].append(y[j * n:(j + 1) * n].double().cpu())
+        at += n
+    for r in range(2):
+        check(torch.cat(got[r]), r, f"portions by tiles, request {r}")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -535,6 +562,22 @@ def test_pages_and_slots_used_again(name, dtype, loaded, plain, tmp_path):
         tt.run_in_process(model, tb, max_tokens, str(d), prepare=tt.poison_free_memory, use_graphs=graphs)
         compare(tt.read_rows(tb, str(d), model.vocab_size), ref, TOL[dtype], f"poisoned {name}/{dtype}",
                 plain.margins(name, dtype))
+
+
+@pytest.mark.parametrize("name", ["a", "c"])
+def test_lightning_by_chunks_inside_the_engine(name, loaded, plain, tmp_path, monkeypatch):
+    """Every step with a portion takes the chunked form of the recurrence (the tests' prompts are shorter than the
+    length from which the engine chooses it by itself), in whole prompts, uneven portions and mixed, padded steps."""
+    from gesso_b200 import ops
+    monkeypatch.setattr(ops, "LIGHTNING_CHUNK_MIN_TOKENS", 2)
+    reqs, ref = plain(name)
+    model = loaded(name, "float32")
+    for sched in ("whole", "portions", "mixed"):
+        tb, max_tokens = SCHEDULES[sched](reqs)
+        for graphs in (False, True):
+            d = str(tmp_path / f"{sched}{int(graphs)}")
+            tt.run_in_process(model, tb, max_tokens, d, prepare=tt.poison_free_memory, use_graphs=graphs)
+            compare(tt.read_rows(tb, d, model.vocab_size), ref, TOL["float32"], f"chunked {name}/{sched}/graphs={graphs}")
 
 
 def test_schedules_agree_float32(loaded, plain, tmp_path):
