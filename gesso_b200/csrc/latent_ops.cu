@@ -17,6 +17,10 @@
 //    q'[h] = W_uk[h]^T q[h] (so that scores are q' . c against the cached latent itself), and the weighted sum of
 //    latents is carried out of it, o[h] = W_uv[h] (sum_j p_j c_j).  float32 accumulation; x, W and out each
 //    float32 or bfloat16.  A block takes 4 rows x 1 head x 128 outputs; x rows sit in shared memory.
+//
+// 3. headwise_linear_tc: the same product on the tensor cores (mma.m16n8k16, bfloat16 in and out, float32
+//    accumulation) for many rows, with the matrices output-major, W [H, O, I]: a block of four warps takes 64 rows x 1
+//    head x 64 outputs, fragments read straight from global memory (the matrices are small and stay in L1/L2).
 #include "common.cuh"
 
 template <typename TO>
@@ -143,5 +147,63 @@ GESSO_API int gesso_headwise_linear(const void* x, int x_dtype, const void* w, i
         default: return GESSO_ERR_BAD_DTYPE;
     }
 #undef GO
+    return launch_status();
+}
+
+// ---- the same on the tensor cores ------------------------------------------------------------------------------------
+__device__ __forceinline__ void hw_mma(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                       unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(128)
+headwise_linear_tc_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ out, int n_rows, int H,
+                          int I, int O) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int h = blockIdx.y, r0 = blockIdx.x * 64 + 16 * warp, n0 = blockIdx.z * 64;
+    if (r0 >= n_rows) return;
+    // rows and outputs past the end repeat the last one (computed, never stored)
+    const int ra = min(r0 + g, n_rows - 1), rb = min(r0 + g + 8, n_rows - 1);
+    const bf16* xa = x + ((size_t)ra * H + h) * I + 2 * t;
+    const bf16* xb = x + ((size_t)rb * H + h) * I + 2 * t;
+    const bf16* wn[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) wn[j] = w + ((size_t)h * O + min(n0 + 8 * j + g, O - 1)) * I + 2 * t;
+    float acc[8][4] = {};
+    for (int k = 0; k < I; k += 16) {
+        const unsigned a0 = *reinterpret_cast<const unsigned*>(xa + k), a1 = *reinterpret_cast<const unsigned*>(xb + k);
+        const unsigned a2 = *reinterpret_cast<const unsigned*>(xa + k + 8), a3 = *reinterpret_cast<const unsigned*>(xb + k + 8);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const unsigned b0 = *reinterpret_cast<const unsigned*>(wn[j] + k), b1 = *reinterpret_cast<const unsigned*>(wn[j] + k + 8);
+            hw_mma(acc[j], a0, a1, a2, a3, b0, b1);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int n = n0 + 8 * j + 2 * t;
+        if (n >= O) continue;                     // O is even: n + 1 < O too
+        if (r0 + g < n_rows)
+            *reinterpret_cast<__nv_bfloat162*>(out + ((size_t)(r0 + g) * H + h) * O + n) = __floats2bfloat162_rn(acc[j][0], acc[j][1]);
+        if (r0 + g + 8 < n_rows)
+            *reinterpret_cast<__nv_bfloat162*>(out + ((size_t)(r0 + g + 8) * H + h) * O + n) = __floats2bfloat162_rn(acc[j][2], acc[j][3]);
+    }
+}
+
+GESSO_API int gesso_headwise_linear_tc_takes(int I, int O) { return I >= 16 && I % 16 == 0 && O >= 8 && O % 8 == 0; }
+
+// x [n_rows, H, I], w [H, O, I] (output-major), out [n_rows, H, O], all bfloat16.
+GESSO_API int gesso_headwise_linear_tc(const void* x, const void* w, void* out, int n_rows, int H, int I, int O,
+                                       cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (!gesso_headwise_linear_tc_takes(I, O) || H <= 0 || H > 65535 || (O + 63) / 64 > 65535) return GESSO_ERR_BAD_SIZE;
+    if (((size_t)x & 3) || ((size_t)w & 3) || ((size_t)out & 3)) return GESSO_ERR_BAD_SIZE;
+    const dim3 grid((n_rows + 63) / 64, H, (O + 63) / 64);
+    launch_pdl(headwise_linear_tc_kernel, grid, dim3(128), 0, stream, (const bf16*)x, (const bf16*)w, (bf16*)out, n_rows, H,
+               I, O);
     return launch_status();
 }

@@ -42,6 +42,8 @@ _SIGNATURES = {
     "gesso_causal_conv": [P, I, I, P, P, P, LL, P, P, P, P, I, I, I, I, P, I, I, I, F, P],
     "gesso_latent_norm_store": [P, I, I, P, P, F, P, I, P, P, P, I, I, P, I, P, I, P, P],
     "gesso_headwise_linear": [P, I, P, I, P, I, I, I, I, I, P],
+    "gesso_headwise_linear_tc": [P, P, P, I, I, I, I, P],
+    "gesso_headwise_linear_tc_takes": [I, I],
     "gesso_lightning": [P, I, I, P, LL, P, P, P, P, I, I, I, I, I, P],
     "gesso_lightning_chunked": [P, I, I, P, LL, P, P, P, P, P, I, P, P, I, I, I, I, I, P],
     "gesso_lightning_chunked_takes": [I, I],

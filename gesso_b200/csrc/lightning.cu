@@ -557,7 +557,7 @@ GESSO_API long long gesso_lightning_chunked_workspace(int n_tiles, int H, int D,
 
 GESSO_API int gesso_lightning_chunked_takes(int D, int Dv) { return D >= 1 && D <= 128 && Dv >= 1 && Dv <= 128; }
 
-// The same contract as gesso_lightning for a step with prompt portions; tile_seg / tile_q0 [n_tiles]: the step's
+// The same arguments and result as gesso_lightning for a step with prompt portions; tile_seg / tile_q0 [n_tiles]: the step's
 // 64-token query tiles; ws: gesso_lightning_chunked_workspace bytes.
 GESSO_API int gesso_lightning_chunked(const void* proj, int dtype, int row_stride, float* state, long long slot_stride,
                                       const float* decay, const int* seg_start, const int* slots, const int* tile_seg,

@@ -588,6 +588,32 @@ def headwise_linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype) ->
     return out
 
 
+HEADWISE_TC_MIN_ROWS = 64      # fewer rows: the FP32-arithmetic kernel streams the matrices once and is as fast
+
+
+def headwise_linear_tc_takes(n_rows: int, x_dtype, w_out_major: torch.Tensor, out_dtype) -> bool:
+    """Whether the tensor-core per-head product takes this step: bfloat16 in and out, at least 64 rows, inputs in
+    multiples of 16 and outputs in multiples of 8."""
+    H, O, I = w_out_major.shape
+    return (n_rows >= HEADWISE_TC_MIN_ROWS and x_dtype == torch.bfloat16 and out_dtype == torch.bfloat16
+            and w_out_major.dtype == torch.bfloat16 and bool(_lib.library().gesso_headwise_linear_tc_takes(I, O)))
+
+
+def headwise_linear_tc(x: torch.Tensor, w_out_major: torch.Tensor) -> torch.Tensor:
+    """``out[n, h, o] = sum_i w[h, o, i] * x[n, h, i]`` on the tensor cores for per-head matrices ``w`` [H, O, I]
+    (output-major); bfloat16 in and out, float32 accumulation."""
+    _cuda_contig(x, "x", torch.bfloat16)
+    _cuda_contig(w_out_major, "w", torch.bfloat16)
+    N, H, I = x.shape
+    _need(w_out_major.dim() == 3 and w_out_major.shape[0] == H and w_out_major.shape[2] == I,
+          "per-head matrices must be [heads, outputs, inputs]")
+    O = w_out_major.shape[1]
+    out = torch.empty((N, H, O), dtype=torch.bfloat16, device=x.device)
+    _lib.check(_lib.library().gesso_headwise_linear_tc(_p(x), _p(w_out_major), _p(out), N, H, I, O, _stream()),
+               "headwise_linear_tc")
+    return out
+
+
 def lightning_attention(proj: torch.Tensor, state: torch.Tensor, decay: torch.Tensor, seg_start: torch.Tensor,
                         slots: torch.Tensor, n_segs: int, n_heads: int, dim: int, vdim: int) -> torch.Tensor:
     """Linear attention with a per-head decay as a recurrence: ``S = decay * S + k v^T``, ``o = S^T q`` with q, k, v

@@ -97,11 +97,20 @@ class LatentAttention(Mixer):
         # per head, input-major: q' = W_uk[h]^T q ([D, R] as stored), o = W_uv[h] a ([R, Dv]: transposed once)
         self.w_absorb = tensors["uk.weight"].reshape(H, D, R).contiguous()
         self.w_expand = tensors["uv.weight"].reshape(H, Dv, R).transpose(1, 2).contiguous()
+        # the same two output-major, for the tensor-core product that steps of many rows take
+        self.w_absorb_t = self.w_absorb.transpose(1, 2).contiguous()                   # [H, R, D]
+        self.w_expand_t = tensors["uv.weight"].reshape(H, Dv, R).contiguous()          # [H, Dv, R]
         self.sink = tensors["sink"].float().contiguous() if self.has_sink else None
         self.w_o = tensors["o_proj.weight"]
         self.rt = rt
         self.mirror = (rt.dtype == torch.bfloat16 and self.kv_rank in (32, 64, 96, 128) and self.nh <= 16
                        and ops.LATENT_TENSOR_CORES)
+
+    @staticmethod
+    def _per_head(x, w_in_major, w_out_major, out_dtype):
+        if ops.headwise_linear_tc_takes(x.shape[0], x.dtype, w_out_major, out_dtype):
+            return ops.headwise_linear_tc(x, w_out_major)
+        return ops.headwise_linear(x, w_in_major, out_dtype)
 
     def forward(self, x, ctx, cache):
         writes = cache.writes
@@ -112,12 +121,12 @@ class LatentAttention(Mixer):
                                    v_pages=cache.v_pages if self.mirror else None)
         q = ops.linear(cq, self.w_uq, out_dtype=x.dtype).view(-1, self.nh, self.hd)
         if self.mirror:
-            q_lat = ops.headwise_linear(q, self.w_absorb, x.dtype)                        # [N, H, R], an operand
+            q_lat = self._per_head(q, self.w_absorb, self.w_absorb_t, x.dtype)            # [N, H, R], an operand
             a = self.rt.attention(q_lat, cache, ctx, self.window, self.scale, sink=self.sink, split_weights=True)
         else:
             q_lat = ops.headwise_linear(q, self.w_absorb, torch.float32)                  # [N, H, R]
             a = self.rt.attention(q_lat, cache, ctx, self.window, self.scale, sink=self.sink, values_are_keys=True)
-        o = ops.headwise_linear(a.view(-1, self.nh, R), self.w_expand, x.dtype)           # [N, H, Dv]
+        o = self._per_head(a.view(-1, self.nh, R), self.w_expand, self.w_expand_t, x.dtype)   # [N, H, Dv]
         return ops.linear(o.view(-1, self.nh * self.vd), self.w_o, out_dtype=torch.float32), None
 
 

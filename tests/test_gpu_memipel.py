@@ -197,6 +197,14 @@ def test_latent_norm_store_and_headwise_products(dtype):
         got = ops.headwise_linear(x, w, out_dtype).double().cpu()
         want = torch.einsum("nhi,hio->nho", x.double().cpu(), w.double().cpu())
         assert torch.allclose(got, want, atol=tol * 5, rtol=tol)
+    if dtype == torch.bfloat16:             # the tensor-core form: many rows, matrices output-major
+        for N, Hh, I, O in ((64, 2, 16, 8), (333, 3, 48, 72), (2048, 4, 128, 64), (70, 1, 32, 200)):
+            x = torch.randn(N, Hh, I, device=DEV).to(dtype)
+            wt = torch.randn(Hh, O, I, device=DEV).to(dtype)
+            assert ops.headwise_linear_tc_takes(N, x.dtype, wt, dtype)
+            got = ops.headwise_linear_tc(x, wt).double().cpu()
+            want = torch.einsum("nhi,hoi->nho", x.double().cpu(), wt.double().cpu())
+            assert torch.allclose(got, want, atol=0.15, rtol=2e-2), float((got - want).abs().max())
 
 
 def _pages(k, v, page_size, order):
