@@ -4,8 +4,9 @@ float32 runs always take the FP32-arithmetic kernel.  bfloat16 runs take the ten
 when the sizes fit them (head 32/64/96/128, pages in multiples of 16 slots): the split-KV kernel
 for steps of single tokens; for steps with portions the tcgen05 flash kernel (head 64, 2 to 16 query
 heads per kv head) or else the mma.sync flash kernel; other sizes take the FP32-arithmetic kernel
-on bfloat16 data.  A distance bias per head and a sink in the softmax denominator are taken by the mma.sync kernels and the
-FP32-arithmetic kernel; values that are the keys themselves and float32 queries by the FP32-arithmetic kernel only.  Kept first keys under a window, an output gate and attention weights in two
+on bfloat16 data.  A distance bias per head and a sink in the softmax denominator are taken by the mma.sync
+kernels and the FP32-arithmetic kernel; values that are the keys themselves and float32 queries by the
+FP32-arithmetic kernel only.  Kept first keys under a window, an output gate and attention weights in two
 bfloat16 pieces are taken by every kernel (the FP32-arithmetic kernel's weights are float32 anyway);
 values of another width than the keys by the FP32-arithmetic kernel only.  Every
 branch is one of this library's own kernels.

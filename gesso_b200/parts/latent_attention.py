@@ -8,8 +8,8 @@ With the mixer's input ``x`` (own notation; ``N(.; w)`` is an RMS norm with a pl
     p = softmax over the visible keys, with one more term exp(sink_h) in the denominator (``sink``)
     out = W_o concat_h( sum_j p_h(i, j) v_h(j) )
 
-There are no positions in it.  The cache holds ``c`` alone: one "kv head" of ``kv_rank`` features per position and
-no value pages.  The engine evaluates the *absorbed* form, which reads the cached latent directly::
+There are no positions in it.  The cache holds ``c`` alone: one "kv head" of ``kv_rank`` features per position.
+The engine evaluates the *absorbed* form, which reads the cached latent directly::
 
     q'_h = W_uk[h]^T q_h                    (carried into the latent space: kv_rank features, float32)
     a_h  = sum_j p_h(i, j) c(j)             (scores q'_h . c(j); keys and values are the same rows)
@@ -21,15 +21,16 @@ In bfloat16 runs whose sizes the tensor-core attention kernels take (``kv_rank``
 heads) the latent is cached twice, as rows and transposed (the two layouts those kernels read keys and values
 from; still ``2 kv_rank`` numbers per position against ``H (head_dim + v_head_dim)`` of expanded keys and values),
 q' is rounded to bfloat16 as their operand, and the attention weights act on the latents as two bfloat16 pieces.
-Every other size and the float32 run keep one copy and take the FP32-arithmetic kernel with float32 q'.
+Every other size and the float32 run keep one copy (no value pages) and take the FP32-arithmetic kernel with float32
+q'.  The two per-head products run on the tensor cores for bfloat16 steps of 64 rows and more, else on FP32 FMAs.
 
 Parameters: hidden_size, n_heads, head_dim, v_head_dim, q_rank, kv_rank, scale, window (``None``: all keys), sink
 (default true), norm_eps.  Tensors: ``dq.weight`` [q_rank, hidden], ``dq_norm.weight`` [q_rank], ``uq.weight`` [H *
 head_dim, q_rank], ``dkv.weight`` [kv_rank, hidden], ``dkv_norm.weight`` [kv_rank], ``uk.weight`` [H * head_dim,
 kv_rank], ``uv.weight`` [H * v_head_dim, kv_rank], ``sink`` [H], ``o_proj.weight`` [hidden, H * v_head_dim].
 
-What is 32-bit whatever the run type: both latent norms (on the float32 sums of the down projection), q', the
-scores, the softmax with its sink, and the weighted sum of latents.
+What is 32-bit whatever the run type: both latent norms (on the float32 sums of the down projection), the scores, the
+softmax with its sink, and the weights' action on the latents (float32 products, or two bfloat16 pieces per weight).
 """
 from __future__ import annotations
 
