@@ -693,7 +693,7 @@ def random_memipel_config(seed):
     return cfg, [rng.choice([1, 2, 5, 17, 33, 64, 65, 70, 97, 130]) for _ in range(4)]
 
 
-@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6, 7, 8, 9, 10])
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 13, 15, 17])
 def test_random_configuration_replays_like_plain(seed, tmp_path):
     import gesso_b200
     cfg, lengths = random_memipel_config(seed)
@@ -702,13 +702,15 @@ def test_random_configuration_replays_like_plain(seed, tmp_path):
     plain_model = pm.PlainMemipel.from_dir(d)
     reqs = tt.make_requests(cfg["vocab"], lengths, seed=seed)
     ref = [plain_model.logits(t).numpy() for t in reqs]
-    for dtype in ("float32",):
+    margins = [plain_model.margins(t).numpy() for t in reqs] if seed % 2 else None      # bfloat16 for every other seed
+    for dtype in ("float32", "bfloat16") if margins is not None else ("float32",):
         model = gesso_b200.load(d, dtype=dtype, max_positions=256)
         for name, make in SCHEDULES.items():
             tb, max_tokens = make(reqs)
             out = str(tmp_path / f"{dtype}_{name}")
             tt.run_in_process(model, tb, max_tokens, out)
-            compare(tt.read_rows(tb, out, cfg["vocab"]), ref, TOL[dtype], f"seed {seed} {name} {dtype} {cfg}")
+            compare(tt.read_rows(tb, out, cfg["vocab"]), ref, TOL[dtype], f"seed {seed} {name} {dtype} {cfg}",
+                    margins if dtype == "bfloat16" else None)
         del model
 
 
