@@ -139,6 +139,8 @@ class MemipelLightning:
     def from_json(m, what):
         heads, dim = _int(m, "heads", what), _int(m, "dim", what)
         decay = m.get("decay")
+        if isinstance(decay, (int, float)) and not isinstance(decay, bool):
+            decay = [decay] * heads                      # one number for all heads
         if not isinstance(decay, list) or len(decay) != heads or \
                 any(isinstance(d, bool) or not isinstance(d, (int, float)) for d in decay):
             raise invalid(f"Memipel config: {what}.decay must list one number per head")

@@ -734,6 +734,52 @@ def test_stacks_of_one_kind_of_cache(which, tmp_path):
         del model
 
 
+def test_layer_widths_of_a_real_model():
+    """Width 1,024, 16 heads, a latent of 128, 16 experts: a prompt of 1,300 tokens takes the paths that only large
+    steps take (tcgen05 products, experts grouped by expert, lightning by chunks, the tensor-core attention kernels
+    with a sink and with a distance bias, per-head products on the tensor cores).  Cut into portions the float32
+    engine gives the same logits as in one step; the bfloat16 engine agrees with the float32 one within rounding
+    (the median row well within a hundredth; single rows may sit on a router's close call)."""
+    import gesso_b200
+    from gesso_b200.engine.batch import StepEntry
+    from gesso_b200.engine.trace import make_engine
+    moe = {"kind": "moe", "expert": {"ff": 512, "limit": 7.0}, "router": {"experts": 16, "top": 4, "groups": {"count": 4, "keep": 2}},
+           "shared": {"ff": 512, "limit": 7.0}}
+    layers = [cm.lightning(16, 64, 64, [1.0 - 2.0 ** -(1 + h / 2) for h in range(16)], {"kind": "dense", "ff": 2048}),
+              cm.latent(16, 64, 64, 384, 128, 0.125, 1024, moe),
+              cm.attention(16, 4, 64, 64, 0.125, 3, 1024, True, moe),
+              cm.lightning(16, 64, 64, [1.0 - 2.0 ** -(1 + h / 2) for h in range(16)], moe),
+              cm.attention(16, 4, 64, 64, 0.125, 3, 1024, True, moe)]
+    cfg = {"architecture": "Memipel", "vocab": 1024, "width": 1024, "norm": {"eps": 1e-6}, "layers": layers}
+    T = 1300
+    toks = tt.make_requests(1024, [T], seed=1)[0]
+    want = list(range(0, T, 37)) + [T - 1]
+    res = {}
+    for dtype in ("float32", "bfloat16"):
+        model = gesso_b200.random_model(cfg, seed=0, dtype=dtype, max_positions=2048, style="fan_in")
+        for mode, cuts in (("whole", [T]), ("portions", [1100, 2, 64, 100, 1, 1, 30, 2])):
+            eng = make_engine(model, 2048)
+            eng.admit("a")
+            rows, at = [], 0
+            for c in cuts:
+                w = [p - at for p in want if at <= p < at + c]
+                lg = eng.step([StepEntry("a", toks[at:at + c], w)])
+                if w:
+                    rows.append(lg.float().cpu().numpy().copy())
+                at += c
+            eng.check_status()
+            eng.release("a")
+            res[(dtype, mode)] = np.concatenate(rows, 0)
+        del model
+        torch.cuda.empty_cache()
+    ref = res[("float32", "whole")]
+    errs = lambda a: np.array([row_error(x, y) for x, y in zip(a, ref)])
+    assert errs(res[("float32", "portions")]).max() <= 2e-5
+    for mode in ("whole", "portions"):
+        e = errs(res[("bfloat16", mode)])
+        assert np.median(e) <= 0.012 and np.percentile(e, 80) <= 0.03, (mode, float(np.median(e)), float(e.max()))
+
+
 def test_trace_program_on_a_model_folder(mmp_dirs, plain, tmp_path):
     reqs, ref = plain("b")
     tb, max_tokens = tt.trace_mixed(reqs, seed=2)
