@@ -14,7 +14,8 @@
 // u < keep_first)); a caller's scale instead of 1/sqrt(hd) (the scale is always passed in); an output gate:
 // the result is multiplied by sigmoid(gate[t, h * vd + j]) before it is stored (`gate` rows are
 // `gate_stride` elements apart, e.g. further columns of the fused projection); a learned sink per query head
-// (`sink`: one more term exp(sink[h]) in the softmax denominator, with no key and no value, not scaled); a
+// (`sink`: exp(sink[h]) is added to the softmax denominator: it takes weight away from every key and contributes
+// nothing to the result; the score scale is not applied to it); a
 // distance bias per query head (`slopes`: slopes[h] * (p - u) is taken off the score of key u); values that ARE
 // the keys (`v_from_k`: the weighted sum runs over the key rows themselves, as latent attention in its absorbed
 // form wants: one shared latent per position is key and value of every head); queries and results in float32
@@ -83,7 +84,7 @@ paged_attention_generic_kernel(const TQ* __restrict__ q, const T* __restrict__ k
     if (sink) M = fmaxf(M, sink[h]);
     const float f = (m == -INFINITY) ? 0.f : expf(m - M);
     float L = warp_sum(l * f);
-    if (sink) L += expf(sink[h] - M);                // the sink counts once, with no value
+    if (sink) L += expf(sink[h] - M);                // the sink enters the denominator only
     TQ* orow = out + ((size_t)t * nh + h) * vd;
     const T* grow = gate ? gate + (size_t)t * gate_stride + (size_t)h * vd : nullptr;
 #pragma unroll

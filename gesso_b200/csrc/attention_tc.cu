@@ -413,7 +413,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
         }
         const int head = kvh * G + r;
         if (used == 1) {
-            // a sink: one more term exp(sink) in the denominator, with no key and no value (base-2 domain here)
+            // a sink: exp(sink) is added to the denominator and to nothing else (base-2 domain here)
             if (sink) L += exp2f(sink[head] * LOG2E - M);
             out[((size_t)tok * nh + head) * HD + d] =
                 __float2bfloat16_rn(acc / L * gate_of(gate, (size_t)tok * gate_stride + (size_t)head * HD + d));

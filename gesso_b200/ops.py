@@ -463,7 +463,7 @@ def paged_attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: tor
     """FP32-arithmetic attention over the pages.  ``keep_first``: with a window, the first positions of the
     sequence that stay visible.  ``gate``: a 2-D view ``[N, nh * value size]`` with unit column stride (columns of
     the fused projection, say) whose sigmoid multiplies the result.  ``sink``: float32 [nh], one more term
-    ``exp(sink[h])`` in the softmax denominator (no key, no value, not scaled).  ``slopes``: float32 [nh],
+    ``exp(sink[h])`` in the softmax denominator (it contributes nothing to the result; ``scale`` is not applied to it).  ``slopes``: float32 [nh],
     ``slopes[h] * (i - j)`` is taken off the score of key j for the query at i.  ``values_are_keys``: the weighted
     sum runs over the key rows (``v_pages`` is not read): the absorbed form of latent attention.  ``q`` may be
     float32 over bfloat16 pages; the result has the type of ``q``."""
