@@ -7,8 +7,8 @@ of three kinds, chosen per layer by ``type``:
 * ``latent_attention``: queries and keys/values through low-rank latents, no positions, a sliding window and a
   learned sink per head in the softmax denominator; only the key/value latent is cached;
 * ``attention``: grouped-query attention with biased projections, a short causal convolution over time on q, k and
-  v, a linear distance bias per head instead of a rotation, a sliding window, and values that later layers mix with
-  the first such layer's values of the same token;
+  v, a linear distance bias per head instead of a rotation, a sliding window, and value mixing: the earliest layer
+  that mixes is the source, every later one blends its own values of a token with the source's for that token;
 * ``lightning``: linear attention with a fixed decay per head, a float32 state per request, a norm over the
   concatenated heads and a sigmoid gate.
 

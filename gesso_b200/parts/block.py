@@ -12,7 +12,7 @@ path, src/Inference/Inference.jl:3239-3247).
 
 ``sandwich``: each sublayer's output is normed once more before it is added (see :class:`SandwichBlock`).
 
-``parallel``: one norm, whose output both sublayers read (see :class:`ParallelBlock`).
+``parallel``: a single norm feeds the mixer and the feed-forward alike (see :class:`ParallelBlock`).
 """
 from __future__ import annotations
 
@@ -141,7 +141,7 @@ class SandwichBlock:
 
 
 class ParallelBlock:
-    """One norm per layer, and both sublayers read its output::
+    """A single norm per layer feeds the mixer and the feed-forward alike::
 
         n = Norm(h);   h = h + (Mixer(n) + FeedForward(n))        (the feed-forward may be left out)
 
